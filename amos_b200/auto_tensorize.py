@@ -214,6 +214,12 @@ class ScheduleGenerator:
     def num_entries(self) -> int:
         return len(self.entries)
 
+    def has_entry(self) -> bool:
+        return bool(self.entries)
+
+    def topk(self, k: int = 1):
+        return self.entries[:k]
+
     def num_foreign_entries(self) -> int:
         return sum(1 for e in self.entries if e.record.foreign)
 
@@ -494,12 +500,6 @@ class CUDAScheduleGeneratorV2(ScheduleGenerator):
 
     def get_schedule_compute_info(self) -> ScheduleComputeInfo:
         return ScheduleComputeInfo(self.target_dag, self.desc)
-
-    def has_entry(self) -> bool:
-        return bool(self.entries)
-
-    def topk(self, k: int = 1):
-        return self.entries[:k]
 
 
 class CUDAScheduleApplierV2(ScheduleApplier):

@@ -1,4 +1,3 @@
 """`tvm.tensor_graph`: only the auto-tensorize dispatcher contract
 (reference: python/tvm/tensor_graph/core/auto_schedule/auto_schedule.py:92-105, 351-433)."""
-from ...tensor_graph import AutoTensorizeContext, auto_tensorize_cuda  # noqa: F401
-from . import core  # noqa: F401
+from ...dispatch import AutoTensorizeContext, auto_tensorize_cuda  # noqa: F401

@@ -1,3 +1,3 @@
 """Same module path as the reference's dispatcher
 (python/tvm/tensor_graph/core/auto_schedule/auto_schedule.py)."""
-from .....tensor_graph import AutoTensorizeContext, auto_tensorize_cuda  # noqa: F401
+from .....dispatch import AutoTensorizeContext, auto_tensorize_cuda  # noqa: F401
