@@ -124,6 +124,43 @@ _SIGNATURES = {
                                                 ctypes.c_void_p]),
 }
 
+
+
+class AmosbDLContext(ctypes.Structure):
+    _fields_ = [("device_type", ctypes.c_int32), ("device_id", ctypes.c_int32)]
+
+
+class AmosbDLDataType(ctypes.Structure):
+    _fields_ = [("code", ctypes.c_uint8), ("bits", ctypes.c_uint8), ("lanes", ctypes.c_uint16)]
+
+
+class AmosbDLTensor(ctypes.Structure):
+    """Layout of the DLTensor of the DLPack release the reference vendors (48 bytes)."""
+    _fields_ = [("data", ctypes.c_void_p), ("ctx", AmosbDLContext), ("ndim", ctypes.c_int32),
+                ("dtype", AmosbDLDataType), ("shape", ctypes.POINTER(ctypes.c_int64)),
+                ("strides", ctypes.POINTER(ctypes.c_int64)), ("byte_offset", ctypes.c_uint64)]
+
+
+class AmosbTVMValue(ctypes.Union):
+    _fields_ = [("v_int64", ctypes.c_int64), ("v_float64", ctypes.c_double),
+                ("v_handle", ctypes.c_void_p), ("v_str", ctypes.c_char_p),
+                ("v_type", AmosbDLDataType), ("v_ctx", AmosbDLContext)]
+
+
+DL_GPU, DL_INT, DL_FLOAT, DL_BFLOAT = 2, 0, 2, 4
+TVM_NULLPTR, TVM_DLTENSOR_HANDLE, TVM_NDARRAY_HANDLE = 4, 7, 13
+DL_DTYPES = {AMOSB_F16: (DL_FLOAT, 16), AMOSB_F32: (DL_FLOAT, 32), AMOSB_S8: (DL_INT, 8),
+             AMOSB_S32: (DL_INT, 32), AMOSB_BF16: (DL_BFLOAT, 16)}
+
+_SIGNATURES.update({
+    "amosb_sync_check": (ctypes.c_int, [ctypes.c_int]),
+    "amosb_set_stream": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p]),
+    "amosb_packed_call": (ctypes.c_int, [ctypes.POINTER(AmosbTVMValue),
+                                         ctypes.POINTER(ctypes.c_int), ctypes.c_int,
+                                         ctypes.POINTER(AmosbTVMValue),
+                                         ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]),
+})
+
 STATIC_SCRATCH_BYTES = 8 * 1024 * 1024  # AMOSB_STATIC_SCRATCH_BYTES
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
@@ -175,6 +212,43 @@ def make_tensor(data_ptr: int, device_id: int, dtype: int, shape: Sequence[int],
     t.strides = ctypes.cast(st, ctypes.POINTER(ctypes.c_int64)) if st is not None else None
     t.byte_offset = byte_offset
     return t, (shp, st)
+
+
+def make_dl_tensor(data_ptr: int, device_id: int, dtype: int, shape: Sequence[int],
+                   strides: Sequence[int] | None = None, byte_offset: int = 0,
+                   device_type: int = DL_GPU, lanes: int = 1):
+    """Build an AmosbDLTensor (the reference's DLTensor layout); returns (struct, keepalive)."""
+    nd = len(shape)
+    shp = (ctypes.c_int64 * max(nd, 1))(*shape)
+    st = (ctypes.c_int64 * max(nd, 1))(*strides) if strides is not None else None
+    t = AmosbDLTensor()
+    t.data = data_ptr
+    t.ctx.device_type, t.ctx.device_id = device_type, device_id
+    t.ndim = nd
+    t.dtype.code, t.dtype.bits = DL_DTYPES[dtype]
+    t.dtype.lanes = lanes
+    t.shape = ctypes.cast(shp, ctypes.POINTER(ctypes.c_int64))
+    t.strides = ctypes.cast(st, ctypes.POINTER(ctypes.c_int64)) if st is not None else None
+    t.byte_offset = byte_offset
+    return t, (shp, st)
+
+
+def packed_call(desc: AmosbOpDesc, dl_tensors: Sequence[AmosbDLTensor],
+                type_codes: Sequence[int] | None = None) -> int:
+    """Enter the library the way a reference build enters its generated code: TVMValue array,
+    type codes, the descriptor as resource handle.  Returns the raw return code (0 or -1)."""
+    n = len(dl_tensors)
+    vals = (AmosbTVMValue * max(n, 1))()
+    for i, t in enumerate(dl_tensors):
+        vals[i].v_handle = ctypes.addressof(t) if t is not None else None
+    codes = (ctypes.c_int * max(n, 1))(*(type_codes or [TVM_DLTENSOR_HANDLE] * n))
+    ret = AmosbTVMValue()
+    ret_code = ctypes.c_int(-7)
+    rc = load().amosb_packed_call(vals, codes, n, ctypes.byref(ret), ctypes.byref(ret_code),
+                                  ctypes.cast(ctypes.byref(desc), ctypes.c_void_p))
+    if rc == 0:
+        assert ret_code.value == TVM_NULLPTR
+    return rc
 
 
 def recognize(te_dag_text: str) -> AmosbOpDesc:

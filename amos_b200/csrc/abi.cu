@@ -147,6 +147,34 @@ static int check_tensor(const AmosbTensor& t, const Expect& e, const char* name,
   return AMOSB_OK;
 }
 
+// A tensor handed to amosb_run is encoded into a tensor map and read by the copy engine: a host
+// pointer or a pointer into another GPU's memory would fault the context.  The reference's generated
+// host function asserts device_type for the same reason (reference:
+// src/tir/transforms/arg_binder.cc:285-286); AmosbTensor has no such field, so the runtime is asked.
+static int check_residency(const AmosbTensor& t, const char* name) {
+  cudaPointerAttributes attr;
+  const void* p = static_cast<const uint8_t*>(t.data) + t.byte_offset;
+  cudaError_t e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // not sticky: leave the runtime's error state clean
+    set_error("CUDA error %d (%s): cannot query the memory of argument %s", (int)e,
+              cudaGetErrorName(e), name);
+    return AMOSB_ERR_CUDA;
+  }
+  const bool on_gpu = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+  if (!on_gpu) {
+    set_error("Argument %s.device_type is expected to be cuda: data is %s memory", name,
+              attr.type == cudaMemoryTypeHost ? "pinned host" : "pageable host");
+    return AMOSB_ERR_ARG;
+  }
+  if (attr.type == cudaMemoryTypeDevice && attr.device != t.device_id) {
+    set_error("Argument %s: data lives on device %d, device_id says %d", name, attr.device,
+              t.device_id);
+    return AMOSB_ERR_ARG;
+  }
+  return AMOSB_OK;
+}
+
 static inline void* tensor_ptr(const AmosbTensor& t) {
   return static_cast<uint8_t*>(t.data) + t.byte_offset;
 }
@@ -190,6 +218,11 @@ static int validate_call(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_
               ins[0].device_id, ins[1].device_id, outs[0].device_id);
     return AMOSB_ERR_ARG;
   }
+  if (on_device) {
+    if ((rc = check_residency(A, names[desc->arg_a])) != AMOSB_OK) return rc;
+    if ((rc = check_residency(B, names[desc->arg_b])) != AMOSB_OK) return rc;
+    if ((rc = check_residency(outs[0], names[want_in])) != AMOSB_OK) return rc;
+  }
   if (has_addend) {
     const AmosbTensor& D = ins[desc->arg_c];
     Expect ed = ec;
@@ -206,6 +239,7 @@ static int validate_call(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_
       set_error("Argument device_id mismatch: all tensors must be on one device");
       return AMOSB_ERR_ARG;
     }
+    if (on_device && (rc = check_residency(D, names[desc->arg_c])) != AMOSB_OK) return rc;
     if (pc) *pc = &D;
   } else if (pc) {
     *pc = nullptr;
@@ -264,6 +298,7 @@ int64_t amosb_workspace_bytes(const AmosbOpDesc* desc) {
 
 int amosb_run(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in, AmosbTensor* outs,
               int n_out, void* workspace, int64_t workspace_bytes, void* cuda_stream) {
+  NvtxRange range("amosb_run");
   const AmosbTensor *A = nullptr, *B = nullptr, *D = nullptr;
   int rc = validate_call(desc, ins, n_in, outs, n_out, true, &A, &B, &D);
   if (rc != AMOSB_OK) return rc;
@@ -296,7 +331,7 @@ struct HostPathArena {
   size_t cap[5] = {0, 0, 0, 0, 0};
 };
 static HostPathArena g_arena[64];
-static std::mutex g_arena_mutex;
+static std::mutex g_arena_mutex[64];  // one per device: calls on different GPUs do not serialise
 
 static int arena_reserve(HostPathArena& ar, int slot, size_t bytes) {
   if (bytes == 0) bytes = 16;
@@ -319,6 +354,7 @@ struct HostPathStreams {
   bool ready = false;
   cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
   cudaEvent_t arrived[kMaxChunks], computed[kMaxChunks];
+  int* status_host = nullptr;  // pinned landing place of the device's status word
 };
 static HostPathStreams g_host_streams[64];
 
@@ -332,6 +368,8 @@ static int host_streams(int device, HostPathStreams** out) {
       AMOSB_CUDA_CHECK(cudaEventCreateWithFlags(&hs.arrived[i], cudaEventDisableTiming));
       AMOSB_CUDA_CHECK(cudaEventCreateWithFlags(&hs.computed[i], cudaEventDisableTiming));
     }
+    AMOSB_CUDA_CHECK(cudaHostAlloc(&hs.status_host, sizeof(int), cudaHostAllocDefault));
+    *hs.status_host = 0;
     hs.ready = true;
   }
   *out = &hs;
@@ -353,6 +391,7 @@ static int host_chunks(const AmosbOpDesc& d, int64_t units, size_t sliced_bytes)
 
 int amosb_run_host(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in, AmosbTensor* outs,
                    int n_out, int device) {
+  NvtxRange range("amosb_run_host");
   const AmosbTensor *A = nullptr, *B = nullptr, *D = nullptr;
   int rc = validate_call(desc, ins, n_in, outs, n_out, false, &A, &B, &D);
   if (rc != AMOSB_OK) return rc;
@@ -363,7 +402,7 @@ int amosb_run_host(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in, Am
   AMOSB_CUDA_CHECK(cudaSetDevice(device));
   const int64_t ws_bytes = amosb_workspace_bytes(desc);
   if (ws_bytes < 0) return (int)ws_bytes;
-  std::lock_guard<std::mutex> lock(g_arena_mutex);
+  std::lock_guard<std::mutex> lock(g_arena_mutex[device]);
   HostPathArena& ar = g_arena[device];
   size_t in_bytes[3] = {0, 0, 0};
   for (int i = 0; i < n_in; ++i) {
@@ -464,12 +503,174 @@ int amosb_run_host(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in, Am
                                      dout[0].data, (size_t)cnt * out_unit, cudaMemcpyDeviceToHost,
                                      hs->out));
   }
+  // the status word follows the last output copy, so the caller never gets numbers from a kernel
+  // that gave up a wait together with a success code
+  int* status_dev = device_status_ptr(device);
+  if (status_dev != nullptr) {
+    AMOSB_CUDA_CHECK(cudaMemcpyAsync(hs->status_host, status_dev, sizeof(int),
+                                     cudaMemcpyDeviceToHost, hs->out));
+  }
   AMOSB_CUDA_CHECK(cudaStreamSynchronize(hs->out));
   set_launch_count(launches);
+  if (status_dev != nullptr && *hs->status_host != 0) {
+    const int code = *hs->status_host;
+    *hs->status_host = 0;
+    status_peek(device, 1);  // clear the word for the next call
+    set_error("a device-side wait ran out (status %d): the output is not valid", code);
+    return AMOSB_ERR_DEVICE_TIMEOUT;
+  }
   return AMOSB_OK;
 }
 
 int amosb_status_peek(int device, int clear) { return status_peek(device, clear); }
+
+int amosb_sync_check(int device) {
+  const int v = status_peek(device, 1);
+  if (v < 0) return v;  // the peek itself failed; its message stands
+  if (v != 0) {
+    set_error("a device-side wait ran out (status %d: %s); results of kernels launched since the "
+              "last check are not valid",
+              v,
+              v == 101   ? "a copy-issuing thread waited for a free stage"
+              : v == 102 ? "the MMA thread waited for a filled stage"
+              : v == 103 ? "the MMA thread waited for a drained accumulator"
+              : v == 104 ? "an epilogue warp waited for a finished accumulator"
+              : v == 105 ? "teardown waited for copies in flight"
+                         : "unknown code");
+    return AMOSB_ERR_DEVICE_TIMEOUT;
+  }
+  return AMOSB_OK;
+}
+
+// ---- the reference's calling convention -------------------------------------------------------
+static thread_local void* g_packed_stream[64] = {nullptr};
+
+int amosb_set_stream(int device, void* cuda_stream) {
+  if (device < 0 || device >= 64) {
+    set_error("device id %d out of range", device);
+    return AMOSB_ERR_ARG;
+  }
+  g_packed_stream[device] = cuda_stream;
+  return AMOSB_OK;
+}
+
+// Scratch of the packed entry point, per device, grown on demand (the reference's generated code
+// gets it from TVMBackendAllocWorkspace and frees it before returning).
+struct PackedScratch {
+  void* buf = nullptr;
+  size_t cap = 0;
+};
+static PackedScratch g_packed_scratch[64];
+static std::mutex g_packed_mutex[64];
+
+static int packed_fail(int code) {
+  // the reference's convention is 0 / -1; the library's own code goes in front of the message
+  char msg[1024];
+  snprintf(msg, sizeof(msg), "[amosb %d] %s", code, last_error());
+  set_error("%s", msg);
+  return -1;
+}
+
+static int dl_dtype_code(const AmosbDLDataType& t) {
+  if (t.lanes != 1) return -1;
+  if (t.code == AMOSB_DL_FLOAT && t.bits == 16) return AMOSB_F16;
+  if (t.code == AMOSB_DL_FLOAT && t.bits == 32) return AMOSB_F32;
+  if (t.code == AMOSB_DL_INT && t.bits == 8) return AMOSB_S8;
+  if (t.code == AMOSB_DL_INT && t.bits == 32) return AMOSB_S32;
+  if (t.code == AMOSB_DL_BFLOAT && t.bits == 16) return AMOSB_BF16;
+  return -1;
+}
+
+int amosb_packed_call(AmosbTVMValue* args, int* type_codes, int num_args,
+                      AmosbTVMValue* out_ret_value, int* out_ret_tcode, void* resource_handle) {
+  const AmosbOpDesc* desc = static_cast<const AmosbOpDesc*>(resource_handle);
+  if (desc == nullptr || args == nullptr || type_codes == nullptr) {
+    set_error("NULL descriptor (resource_handle), argument list or type codes");
+    return packed_fail(AMOSB_ERR_ARG);
+  }
+  const bool has_addend = (desc->epilogue & (AMOSB_EPI_ADD_VECTOR | AMOSB_EPI_ADD_FULL)) != 0;
+  const int want = has_addend ? 4 : 3;
+  if (num_args != want) {
+    set_error("__tvm_main__: num_args should be %d, got %d", want, num_args);
+    return packed_fail(AMOSB_ERR_ARG);
+  }
+  AmosbTensor t[4];
+  int device = -1;
+  for (int i = 0; i < num_args; ++i) {
+    if (type_codes[i] != AMOSB_TVM_DLTENSOR_HANDLE && type_codes[i] != AMOSB_TVM_NDARRAY_HANDLE) {
+      set_error("__tvm_main__: Expect arg[%d] to be pointer (type code %d given)", i,
+                type_codes[i]);
+      return packed_fail(AMOSB_ERR_ARG);
+    }
+    const AmosbDLTensor* dl = static_cast<const AmosbDLTensor*>(args[i].v_handle);
+    if (dl == nullptr) {
+      set_error("__tvm_main__: arg[%d] is a NULL tensor handle", i);
+      return packed_fail(AMOSB_ERR_ARG);
+    }
+    if (dl->ctx.device_type != AMOSB_DL_GPU) {
+      set_error("Argument arg%d.device_type has an unsatisfied constraint: expected %d (gpu), got %d",
+                i, AMOSB_DL_GPU, dl->ctx.device_type);
+      return packed_fail(AMOSB_ERR_ARG);
+    }
+    if (device < 0) device = dl->ctx.device_id;
+    if (dl->ctx.device_id != device) {
+      set_error("Argument arg%d.device_id has an unsatisfied constraint: expected %d, got %d", i,
+                device, dl->ctx.device_id);
+      return packed_fail(AMOSB_ERR_ARG);
+    }
+    const int dt = dl_dtype_code(dl->dtype);
+    if (dt < 0) {
+      set_error("arg%d.dtype (code %d, bits %d, lanes %d) is not one this library computes in: "
+                "float16, bfloat16, float32, int8, int32, one lane",
+                i, (int)dl->dtype.code, (int)dl->dtype.bits, (int)dl->dtype.lanes);
+      return packed_fail(AMOSB_ERR_ARG);
+    }
+    t[i].data = dl->data;
+    t[i].device_id = dl->ctx.device_id;
+    t[i].dtype = dt;
+    t[i].ndim = dl->ndim;
+    t[i].shape = dl->shape;
+    t[i].strides = dl->strides;
+    t[i].byte_offset = dl->byte_offset;
+  }
+  if (device < 0 || device >= 64) {
+    set_error("device id %d out of range", device);
+    return packed_fail(AMOSB_ERR_ARG);
+  }
+  const int64_t ws_bytes = amosb_workspace_bytes(desc);
+  if (ws_bytes < 0) return packed_fail((int)ws_bytes);
+  void* ws = nullptr;
+  if (ws_bytes > 0) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) {
+      set_error("cudaSetDevice(%d) failed: %s", device, cudaGetErrorString(e));
+      return packed_fail(AMOSB_ERR_CUDA);
+    }
+    std::lock_guard<std::mutex> lock(g_packed_mutex[device]);
+    PackedScratch& sc = g_packed_scratch[device];
+    if (sc.cap < (size_t)ws_bytes + 1024) {
+      if (sc.buf) {
+        cudaDeviceSynchronize();  // kernels queued earlier may still use the smaller buffer
+        cudaFree(sc.buf);
+        sc.buf = nullptr;
+        sc.cap = 0;
+      }
+      e = cudaMalloc(&sc.buf, (size_t)ws_bytes + 1024);
+      if (e != cudaSuccess) {
+        set_error("cudaMalloc(%lld) failed: %s", (long long)ws_bytes + 1024, cudaGetErrorString(e));
+        return packed_fail(AMOSB_ERR_CUDA);
+      }
+      sc.cap = (size_t)ws_bytes + 1024;
+    }
+    ws = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(sc.buf) + 1023) & ~uintptr_t(1023));
+  }
+  const int rc = amosb_run(desc, t, num_args - 1, &t[num_args - 1], 1, ws, ws_bytes,
+                           g_packed_stream[device]);
+  if (rc != AMOSB_OK) return packed_fail(rc);
+  if (out_ret_tcode != nullptr) *out_ret_tcode = AMOSB_TVM_NULLPTR;
+  if (out_ret_value != nullptr) out_ret_value->v_handle = nullptr;
+  return 0;
+}
 
 int amosb_last_launch_count(void) { return launch_count(); }
 

@@ -3,8 +3,18 @@
 #include "../../include/amosb.h"
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 namespace amosb {
+
+// Host-side NVTX range around an entry point (a no-op costing a pointer test unless a tool such as
+// Nsight Systems has attached itself to the process).
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 // printf-style; stores the message returned by amosb_last_error() on this thread.
 void set_error(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
@@ -34,6 +44,7 @@ int choose_tile_rows(const AmosbOpDesc& d, int sm_count);  // 128, or 256 for pa
 bool choose_cta_pairs(const AmosbOpDesc& d, int sm_count);
 bool conv_is_pointwise_gemm(const AmosbOpDesc& d);
 int status_peek(int device, int clear);
+int* device_status_ptr(int device);  // device address of the status word, or nullptr
 int device_sm_count(int device);
 void reset_launch_count();
 int launch_count();

@@ -11,6 +11,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -404,6 +405,18 @@ static thread_local int g_launch_count = 0;
 // 3x3 convolutions and by ~1 % on the large GEMMs; never slower.
 static bool dependent_launch_enabled() { return getenv("AMOSB_NO_PDL") == nullptr; }
 
+// Budget of the kernels' bounded waits and the diagnostic that makes one run out; both are read at
+// every launch so that a test can set them around a single call.
+static void set_wait_params(UmmaParams* p) {
+  p->wait_budget_ns = 2000000000ull;
+  if (const char* e = getenv("AMOSB_WAIT_BUDGET_NS")) {
+    const long long v = atoll(e);
+    if (v > 0) p->wait_budget_ns = static_cast<unsigned long long>(v);
+  }
+  const char* d = getenv("AMOSB_DIAG_NO_LOADS");
+  p->diag_no_loads = (d != nullptr && d[0] == '1') ? 1 : 0;
+}
+
 static int producer_threads() {
   int n = 3;
   if (const char* e = getenv("AMOSB_PRODUCERS")) n = atoi(e);
@@ -416,13 +429,14 @@ static int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
                        const UmmaParams& p, int grid, cudaStream_t stream) {
   auto kernel = umma_persistent_kernel<KIND, BN, B_MN, MODE, OutT, EPI, MT, A_MN>;
   constexpr int smem = UmmaConfig<BN, EPI, MT>::kSmemBytes;
-  static bool attr_set[64] = {false};
+  // one bit per device; setting the attribute twice from racing threads is harmless
+  static std::atomic<unsigned long long> attr_set{0};
   int dev = 0;
   AMOSB_CUDA_CHECK(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
+  if (((attr_set.load(std::memory_order_acquire) >> dev) & 1ull) == 0) {
     AMOSB_CUDA_CHECK(
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set[dev] = true;
+    attr_set.fetch_or(1ull << dev, std::memory_order_release);
   }
 #ifdef AMOSB_ROLE_CYCLES
   UmmaParams pd = p;
@@ -522,13 +536,14 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
                        const UmmaParams& p, int pairs, cudaStream_t stream) {
   auto kernel = umma_pair_kernel<KIND, BN, B_MN, MODE, OutT, EPI>;
   constexpr int smem = PairConfig<BN, EPI>::kSmemBytes;
-  static bool attr_set[64] = {false};
+  // one bit per device; setting the attribute twice from racing threads is harmless
+  static std::atomic<unsigned long long> attr_set{0};
   int dev = 0;
   AMOSB_CUDA_CHECK(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
+  if (((attr_set.load(std::memory_order_acquire) >> dev) & 1ull) == 0) {
     AMOSB_CUDA_CHECK(
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set[dev] = true;
+    attr_set.fetch_or(1ull << dev, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -869,6 +884,7 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
 
   UmmaParams p;
   memset(&p, 0, sizeof(p));
+  set_wait_params(&p);
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
@@ -1127,6 +1143,7 @@ int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const voi
 
   UmmaParams p;
   memset(&p, 0, sizeof(p));
+  set_wait_params(&p);
   p.M = (int)Mtot;
   p.N = (int)Kout;
   p.K = (int)Kd;
@@ -1290,6 +1307,7 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   }
   UmmaParams p;
   memset(&p, 0, sizeof(p));
+  set_wait_params(&p);
   p.M = (int)Mtot;
   p.N = (int)Kout;
   p.K = (int)Kd;
@@ -1392,6 +1410,12 @@ int status_peek(int device, int clear) {
     AMOSB_CUDA_CHECK(cudaMemcpy(st->status_ptr, &zero, sizeof(int), cudaMemcpyHostToDevice));
   }
   return v;
+}
+
+int* device_status_ptr(int device) {
+  DeviceState* st = nullptr;
+  if (get_device_state(device, &st) != AMOSB_OK) return nullptr;
+  return st->status_ptr;
 }
 
 int device_sm_count(int device) {

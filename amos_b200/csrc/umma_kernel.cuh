@@ -1,10 +1,12 @@
-// Persistent, warp-specialised tcgen05 kernel shared by GEMM, batched GEMM and NCHW conv2d
-// (implicit GEMM).  One CTA per SM, 192 threads:
-//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor into a ring of smem stages)
-//   warp 1      MMA issuer     (one lane issues tcgen05.mma into one of two TMEM accumulators;
-//                               the warp also owns TMEM alloc/dealloc)
-//   warps 2..5  epilogue       (tcgen05.ld -> registers -> cast -> global stores; overlaps with the
-//                               main loop of the next tile through the second accumulator)
+// Persistent, warp-specialised tcgen05 kernel shared by GEMM, batched GEMM and conv2d (implicit
+// GEMM).  One CTA per SM, 256 threads:
+//   warps 0, 6, 7  TMA producers (one lane each issues cp.async.bulk.tensor into a ring of smem
+//                                 stages; the k-blocks are dealt round-robin)
+//   warp 1         MMA issuer    (one lane issues tcgen05.mma into one of two TMEM accumulators;
+//                                 the warp also owns TMEM alloc/dealloc).  Tall tiles (MT = 2) make
+//                                 warp 7 a second issuer, one per accumulator tile.
+//   warps 2..5     epilogue      (tcgen05.ld -> registers -> cast -> stores; overlaps with the main
+//                                 loop of the next tile through the second accumulator)
 //
 // Tile: 128 (M) x BN (N) x 128 bytes of K per stage (64 fp16 or 128 int8).
 // A is always K-major (rows of K contiguous).  B is either K-major ([N,K], used for the prepacked
@@ -69,6 +71,13 @@ struct UmmaParams {
   int conv_N_real;  // HWNC mode: images that exist (rows past them are computed on zeros, not stored)
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int producers;   // 1..3 threads (in warps 0, 6, 7) issuing the TMA loads, k-blocks dealt round-robin
+  // Nanoseconds after which a wait on an mbarrier is given up (the CTA then raises its abort flag,
+  // records a status code and leaves).  An epilogue wait spans the whole k-loop of a tile, each of
+  // whose own waits has this budget, so it gets twice as much.
+  unsigned long long wait_budget_ns;
+  // Diagnostic: the copy-issuing threads issue no loads and arm no barrier, so that the MMA
+  // thread's first wait runs out with nothing in flight.  The way the give-up path is exercised.
+  int diag_no_loads;
 };
 
 // Output staging of the TMA-store epilogue: per epilogue warp kEpiBufs buffers of 32 rows x 128
@@ -327,7 +336,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     const int pi = warp == 0 ? 0 : warp - 5;
     // stage = pi + j * P below needs P <= kStages
     const int P = min(min(p.producers, kSecondIssuer ? 2 : 3), kStages);
-    if (lane == 0 && pi < P) {
+    if (lane == 0 && pi < P && !p.diag_no_loads) {
       // the kernel may have been started while its predecessor in the stream was still running
       // (for the NCHW conv that is the re-layout kernel that writes both operands): nothing is
       // read from global memory before that kernel has completed
@@ -376,7 +385,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           const long long rc_t0 = clock64();
 #endif
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                         kStatusTimeoutProducer)) {
+                         kStatusTimeoutProducer, p.wait_budget_ns)) {
             ok = false;
             break;
           }
@@ -496,7 +505,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         const long long rc_t1 = clock64();
 #endif
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
-                       kStatusTimeoutMmaTmem)) {
+                       kStatusTimeoutMmaTmem, p.wait_budget_ns)) {
           ok = false;
           break;
         }
@@ -509,7 +518,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t0 = clock64();
 #endif
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutMmaFull)) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutMmaFull, p.wait_budget_ns)) {
             ok = false;
             break;
           }
@@ -582,7 +591,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #ifdef AMOSB_ROLE_CYCLES
       const long long rc_t0 = clock64();
 #endif
-      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kStatusTimeoutEpilogue)) {
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kStatusTimeoutEpilogue, 2 * p.wait_budget_ns)) {
         ok = false;
         break;
       }

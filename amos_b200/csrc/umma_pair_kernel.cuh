@@ -124,7 +124,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // loop only adds and compares (no integer division per k-block): positions advance by P steps.
     const int pi = warp == 0 ? 0 : warp - 5;
     const int P = min(p.producers, kStages);  // stage = pi + j * P below needs P <= kStages
-    if (lane == 0 && pi < P) {
+    if (lane == 0 && pi < P && !p.diag_no_loads) {
       // the kernel may have been started while its predecessor in the stream was still running
       // (for the NCHW conv that is the re-layout kernel that writes both operands): nothing is
       // read from global memory before that kernel has completed
@@ -168,7 +168,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const long long rc_t0 = clock64();
 #endif
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                         kStatusTimeoutProducer)) {
+                         kStatusTimeoutProducer, p.wait_budget_ns)) {
             ok = false;
             break;
           }
@@ -250,7 +250,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const long long rc_t1 = clock64();
 #endif
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status,
-                       kStatusTimeoutMmaTmem)) {
+                       kStatusTimeoutMmaTmem, p.wait_budget_ns)) {
           ok = false;
           break;
         }
@@ -263,7 +263,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t0 = clock64();
 #endif
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutMmaFull)) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kStatusTimeoutMmaFull, p.wait_budget_ns)) {
             ok = false;
             break;
           }
@@ -338,7 +338,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #ifdef AMOSB_ROLE_CYCLES
       const long long rc_t0 = clock64();
 #endif
-      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kStatusTimeoutEpilogue)) {
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kStatusTimeoutEpilogue, 2 * p.wait_budget_ns)) {
         ok = false;
         break;
       }

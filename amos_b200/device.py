@@ -40,15 +40,17 @@ def tensor_arg(t: torch.Tensor):
 
 
 def get_workspace(nbytes: int, device: int) -> torch.Tensor | None:
-    """Cached per-device scratch buffer of at least `nbytes` (1024-byte aligned by the allocator)."""
+    """Cached per-device scratch buffer with at least `nbytes` behind its first 1024-byte boundary.
+    One buffer per device serves every Module and PreparedCall that does not bring its own: calls
+    that use scratch (NCHW conv2d) must be stream-ordered on a device, or pass `workspace=`."""
     if nbytes <= 0:
         return None
     key = (device, 0)
     buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{device}")
-        if buf.data_ptr() % 1024 != 0:  # the caching allocator returns 512-byte multiples
-            buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=f"cuda:{device}")
+    # what counts is the length from the first 1024-byte boundary on (the caching allocator hands
+    # out 512-byte multiples, and PreparedCall rounds the base up)
+    if buf is None or buf.numel() - (-buf.data_ptr() % 1024) < nbytes:
+        buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=f"cuda:{device}")
         _workspaces[key] = buf
     return buf
 
@@ -104,6 +106,12 @@ def run(desc: _lib.AmosbOpDesc, inputs: Sequence[torch.Tensor], outputs: Sequenc
     """Enqueue the operator on `stream` (default: torch's current stream of the tensors' device).
     Returns the number of kernels launched."""
     return PreparedCall(desc, inputs, outputs, stream, workspace).run()
+
+
+def sync_check(device: int = 0) -> None:
+    """Synchronise `device`; raise AmosbError(-4) if a kernel gave up a bounded wait since the last
+    check (its results are then not valid)."""
+    _lib.check(_lib.load().amosb_sync_check(device))
 
 
 def status_peek(device: int = 0, clear: bool = True) -> int:

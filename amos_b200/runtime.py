@@ -164,7 +164,12 @@ class _DeviceSource:
         import os
         here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
         parts = [f"// {self._plan}\n"]
-        for name in ("ptx.cuh", "umma_kernel.cuh"):
+        names = ["ptx.cuh", "umma_kernel.cuh"]  # the pair kernel builds on the single-CTA file
+        if "umma_pair" in self._plan:
+            names.append("umma_pair_kernel.cuh")
+        if "conv_prepack" in self._plan:
+            names.append("launch.cu")  # the re-layout kernels live beside the launchers
+        for name in names:
             path = os.path.join(here, name)
             if os.path.exists(path):
                 with open(path) as f:

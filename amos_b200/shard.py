@@ -3,7 +3,9 @@
 
 * GEMM / int8 GEMM: rows of A and C are split (B is replicated);
 * batched GEMM: the batch is split;
-* conv2d: the images (N) are split (the filter is replicated).
+* conv2d: the images (N) are split (the filter is replicated).  In the HWNC layout the images are
+  the third axis of the activation and of the output: a rank's share is a strided slice, which is
+  copied into a compact tensor once, outside any timed path (the library takes compact tensors only).
 
 The reference has no multi-device path at all (its "remote" measurement is TVM RPC to a single
 device, reference: python/tvm/auto_tensorize/search/measure.py:793-981); this module is the one
@@ -34,10 +36,6 @@ def shard_axis_extent(desc: _lib.AmosbOpDesc) -> int:
         return int(desc.m)
     if desc.kind == _lib.OP_BATCHED_GEMM:
         return int(desc.batch)
-    if desc.kind == _lib.OP_CONV2D_HWNC:
-        raise _lib.AmosbError(_lib.AMOSB_ERR_UNSUPPORTED,
-                              "HWNC tensors have the images in the third dimension: a rank's share "
-                              "is not a contiguous slice; shard the NHWC or NCHW form instead")
     if desc.kind in _lib.CONV_KINDS:
         return int(desc.conv_n)
     raise _lib.AmosbError(_lib.AMOSB_ERR_ARG, f"descriptor has no operator kind ({desc.kind})")
@@ -46,8 +44,6 @@ def shard_axis_extent(desc: _lib.AmosbOpDesc) -> int:
 def local_desc(desc: _lib.AmosbOpDesc, world: int, rank: int) -> tuple[_lib.AmosbOpDesc, int, int]:
     """Descriptor of the part of `desc` that `rank` computes, with (start, count) along the sharded
     axis.  count may be 0 (more ranks than units): the caller then skips the launch."""
-    if world == 1 and rank == 0 and desc.kind == _lib.OP_CONV2D_HWNC:
-        return desc.copy(), 0, int(desc.conv_n)
     start, count = partition(shard_axis_extent(desc), world, rank)
     d = desc.copy()
     if desc.kind == _lib.OP_GEMM:
@@ -67,26 +63,43 @@ def shard_arrays(desc: _lib.AmosbOpDesc, inputs: Sequence, outputs: Sequence, wo
     d, start, count = local_desc(desc, world, rank)
     ins = list(inputs)
     sl = slice(start, start + count)
+    has_addend = bool(desc.epilogue & (_lib.EPI_ADD_VECTOR | _lib.EPI_ADD_FULL))
+    if has_addend and desc.epilogue & _lib.EPI_ADD_FULL:
+        # an addend of the output's shape is cut like the output; a vector over N stays whole
+        ins[desc.arg_c] = ins[desc.arg_c][sl]
     if desc.kind == _lib.OP_BATCHED_GEMM:
-        ins = [x[sl] for x in ins]
+        ins[desc.arg_a] = ins[desc.arg_a][sl]
+        ins[desc.arg_b] = ins[desc.arg_b][sl]
     elif desc.kind == _lib.OP_GEMM and desc.trans_a:
         # A is stored [K, M]: a rank's rows of M are columns of it, which the library (compact
         # strides only) cannot take as a view -- the slice is copied once, outside any timed path
-        part = ins[desc.arg_a][:, sl]
-        ins[desc.arg_a] = part.contiguous() if hasattr(part, "contiguous") else \
-            __import__("numpy").ascontiguousarray(part)
+        ins[desc.arg_a] = _compact(ins[desc.arg_a][:, sl])
+    elif desc.kind == _lib.OP_CONV2D_HWNC:
+        ins[desc.arg_a] = _compact(ins[desc.arg_a][:, :, sl])
     else:
         ins[desc.arg_a] = ins[desc.arg_a][sl]
-    outs = [o[sl] for o in outputs]
+    if desc.kind == _lib.OP_CONV2D_HWNC:
+        outs = [o[:, :, sl] for o in outputs]  # strided views: gather_output concatenates along N
+    else:
+        outs = [o[sl] for o in outputs]
     return d, ins, outs
+
+
+def _compact(x):
+    return x.contiguous() if hasattr(x, "contiguous") else \
+        __import__("numpy").ascontiguousarray(x)
 
 
 def gather_output(local_out, desc: _lib.AmosbOpDesc, group=None):
     """All-gather the output shards (a torch tensor per rank, possibly of unequal length along
-    axis 0) into the full output on every rank.  Outside the timed compute path."""
+    the sharded axis: axis 0, or the image axis 2 of an HWNC output) into the full output on every
+    rank.  Outside the timed compute path."""
     import torch
     import torch.distributed as dist
 
+    if desc.kind == _lib.OP_CONV2D_HWNC:
+        moved = gather_output(local_out.permute(2, 0, 1, 3).contiguous(), _as_nhwc(desc), group)
+        return moved.permute(1, 2, 0, 3).contiguous()
     world = dist.get_world_size(group)
     total = shard_axis_extent(desc)
     counts = [partition(total, world, r)[1] for r in range(world)]
@@ -97,3 +110,9 @@ def gather_output(local_out, desc: _lib.AmosbOpDesc, group=None):
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
     return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
+
+
+def _as_nhwc(desc: _lib.AmosbOpDesc) -> _lib.AmosbOpDesc:
+    d = desc.copy()
+    d.kind = _lib.OP_CONV2D_NHWC
+    return d

@@ -7,9 +7,13 @@ One JSON line on stdout (rank 0).  A "step" is one pass of the operator over one
 synthetic operands.  Headline workload: the fp16 GEMM M=N=K=4096 with fp32 accumulation and fp16
 output; the other configurations are measured briefly and reported under "configs".
 
-N > 1: launched by torchrun, one rank per GPU; rows of M (GEMM), the batch (batched GEMM) or the
-images (conv) are split across ranks, no collective on the timed path; `value` = work of all ranks
-divided by the slowest rank's device time.
+N > 1: launched by torchrun, one rank per GPU.  By default the NAMED configuration is split across
+the ranks -- rows of M (GEMM), batches (batched GEMM), images (conv); B / the filter replicated; no
+collective on the timed path ("scaling": "strong") -- `value` = work of all ranks divided by the
+slowest rank's device time; every rank checks its output shard against the same rows of an
+unsharded run on its own GPU ("shard_parity"), and the optional NCCL all-gather of the output is
+timed separately ("gather").  `--scaling weak` gives every rank the named configuration instead;
+under the default that figure is reported as the extra "weak_scaling".
 """
 from __future__ import annotations
 
@@ -158,6 +162,67 @@ def work_and_bytes(desc):
     return ops, float(byt)
 
 
+def ncu_traffic(name):
+    """DRAM bytes (read + write) per launch of the workload's kernels, from the ncu captures that
+    profiles/ncu_traffic.json records; (None, reason) where no capture exists."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)["workloads"]
+    except (OSError, ValueError, KeyError):
+        return None, "profiles/ncu_traffic.json is missing"
+    rec = table.get(name)
+    if rec is None:
+        return None, "no entry for this workload"
+    if rec.get("dram_bytes") is None:
+        return None, rec.get("reason", "not captured")
+    return float(rec["dram_bytes"]), rec.get("source")
+
+
+def measure_int8_library_peak(dev, seconds=1.0):
+    """int8 tensor-core peak of this GPU as the vendor library reaches it: torch._int_mm (cuBLASLt)
+    on 8192^3, best single call (burst) and a back-to-back loop of `seconds` (sustained)."""
+    import torch
+    n = 8192
+    tdev = f"cuda:{dev}"
+    a = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=tdev)
+    b = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=tdev)
+    ops = 2.0 * n ** 3
+    best = None
+    for rhs, label in ((b, "B row-major"), (b.t().contiguous().t(), "B column-major")):
+        try:
+            for _ in range(3):
+                torch._int_mm(a, rhs)
+            torch.cuda.synchronize(dev)
+            burst = float("inf")
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch._int_mm(a, rhs)
+                e1.record()
+                e1.synchronize()
+                burst = min(burst, e0.elapsed_time(e1))
+            reps = max(10, int(seconds * 1e3 / burst))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                torch._int_mm(a, rhs)
+            e1.record()
+            e1.synchronize()
+            sustained = e0.elapsed_time(e1) / reps
+        except Exception as exc:  # the library refused this layout
+            sys.stderr.write(f"torch._int_mm ({label}) failed: {exc}\n")
+            continue
+        rec = {"int8_tops": ops / burst / 1e9, "int8_tops_sustained": ops / sustained / 1e9,
+               "how": f"torch._int_mm (cuBLASLt) 8192^3, {label}: best of 10 (burst) and {reps} "
+                      f"calls back to back (sustained), CUDA events, measured in this run"}
+        if best is None or rec["int8_tops"] > best["int8_tops"]:
+            best = rec
+    del a, b
+    torch.cuda.empty_cache()
+    return best
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -242,10 +307,25 @@ def _dist_env():
     return rank, world, local
 
 
+def _barrier(world, dev):
+    import torch
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+
+
 def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_steps=0,
-                     use_graph=True, scaling="weak"):
+                     use_graph=True, scaling="strong", min_region_s=0.0, check_shard=False,
+                     time_gather=False):
     """Device-resident timing (and optionally the host-buffer end-to-end timing) of one workload
-    on this rank's shard.  Returns a dict of per-rank figures; the caller reduces over ranks."""
+    on this rank's shard.  Returns a dict of per-rank figures; the caller reduces over ranks.
+
+    The K steps are captured once into a CUDA graph.  One replay is the short ("burst") region;
+    with `min_region_s` the graph is then replayed until the timed region lasts at least that long
+    (the "sustained" region: power-capped clocks, the reference's min_repeat_ms = 500 discipline,
+    reference benchmark/amos/mapping_gemm_tensorcore.py:38)."""
     import torch
     from amos_b200 import _lib, device, runtime, shard
 
@@ -262,10 +342,12 @@ def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_st
         full = make_desc(w)
     desc, start, count = shard.local_desc(full, world, rank)
     ops_local, bytes_local = work_and_bytes(desc) if count > 0 else (0.0, 0.0)
-    res = {"ops_local": ops_local, "bytes_local": bytes_local, "ms": 0.0, "launches": 0,
-           "e2e_ms": None, "h2d": 0, "d2h": 0}
+    res = {"ops_local": ops_local, "bytes_local": bytes_local, "ms": 0.0, "burst_ms": 0.0,
+           "passes": 1, "launches": 0, "e2e_ms": None, "h2d": 0, "d2h": 0, "shard_ok": 1.0,
+           "shard_bit_exact": 1.0, "shard_rel_l2": 0.0, "gather_ms": 0.0}
     if count == 0:
-        return res
+        raise SystemExit(f"{name}: more ranks ({world}) than rows / batches / images to split")
+    torch.cuda.nvtx.range_push(f"bench:{name}:setup")
     tdev = f"cuda:{dev}"
     host = make_inputs(w)
     if weak:
@@ -291,19 +373,10 @@ def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_st
     ws = device.get_workspace(_lib.workspace_bytes(desc), dev)
     stream = torch.cuda.current_stream(dev)
     calls = [device.PreparedCall(desc, ins, outs, stream, ws) for ins, outs in sets]
+    torch.cuda.nvtx.range_pop()
     for i in range(max(warmup, 3)):
         res["launches_per_step"] = calls[i % nsets].run()
-    torch.cuda.synchronize(dev)
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        torch.cuda.synchronize(dev)
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    ctx = sampler if sampler is not None else _Null()
-    # The K steps are captured once into a CUDA graph and replayed, so that the timed region holds
-    # the kernels back to back and not the Python launch loop (the per-call host cost is of the
-    # order of the shorter kernels).  Falls back to plain launches if capture is not possible.
+    _barrier(world, dev)
     graph = None
     if use_graph:
         try:
@@ -313,43 +386,96 @@ def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_st
                 for i in range(steps):
                     calls[i % nsets].run(cap)
             graph.replay()  # one untimed replay: uploads the graph
-            torch.cuda.synchronize(dev)
-            if world > 1:
-                import torch.distributed as dist
-                dist.barrier()
-                torch.cuda.synchronize(dev)
         except Exception as exc:  # pragma: no cover - depends on the driver
             sys.stderr.write(f"graph capture failed ({exc}); timing plain launches\n")
             graph = None
-            torch.cuda.synchronize(dev)
-    with ctx:
-        e0.record(stream)
+        _barrier(world, dev)
+
+    def one_pass():
         if graph is not None:
             graph.replay()
         else:
             for i in range(steps):
                 calls[i % nsets].run()
-        e1.record(stream)
-        torch.cuda.synchronize(dev)
-    res["ms"] = e0.elapsed_time(e1)
+
+    def timed(passes, ctx):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        with ctx:
+            e0.record(stream)
+            for _ in range(passes):
+                one_pass()
+            e1.record(stream)
+            torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1)
+
+    torch.cuda.nvtx.range_push(f"bench:{name}:timed")
+    res["burst_ms"] = timed(1, _Null())
+    passes = 1
+    if min_region_s > 0:
+        passes = int(min(50000, max(1, math.ceil(min_region_s * 1e3 / max(res["burst_ms"], 1e-3)))))
+        if world > 1:  # every rank must replay the same number of times
+            import torch.distributed as dist
+            t = torch.tensor([passes], dtype=torch.int64, device=tdev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            passes = int(t.item())
+        _barrier(world, dev)
+        res["ms"] = timed(passes, sampler if sampler is not None else _Null())
+    else:
+        res["ms"] = res["burst_ms"]
+    torch.cuda.nvtx.range_pop()
+    res["passes"] = passes
     res["launch"] = "cuda_graph" if graph is not None else "stream"
-    res["launches"] = steps * res["launches_per_step"]
+    res["launches"] = passes * steps * res["launches_per_step"]
     res["nsets"] = nsets
-    status = device.status_peek(dev)
-    if status != 0:
-        raise RuntimeError(f"device-side wait ran out (status {status}) in {name}")
-    res["checksum"] = float(sets[0][1][0].double().abs().sum().item())
+    device.sync_check(dev)  # raises if a kernel gave up a bounded wait: the numbers would be void
+    local_out = sets[0][1][0]
+
+    if check_shard and world > 1 and not weak:
+        # The rank runs the unsharded operator once on its own GPU (same seed, hence the same
+        # operands) and compares its shard with the same rows / batches / images: no collective.
+        full_ins = [torch.from_numpy(np.ascontiguousarray(x)).to(tdev) for x in host]
+        full_out = torch.empty(out_shape(full), dtype=out_dtype, device=tdev)
+        device.PreparedCall(full, full_ins, [full_out], stream,
+                            device.get_workspace(_lib.workspace_bytes(full), dev)).run()
+        calls[0].run()  # the shard again, after the workspace may have been replaced
+        torch.cuda.synchronize(dev)
+        want = full_out[start:start + count]
+        exact = bool(torch.equal(local_out, want))
+        rel = 0.0
+        if not exact:
+            diff = (local_out.double() - want.double()).norm()
+            rel = float(diff / want.double().norm().clamp_min(1e-300))
+        integer = desc.out_dtype == _lib.AMOSB_S32
+        res["shard_bit_exact"] = 1.0 if exact else 0.0
+        res["shard_rel_l2"] = rel
+        # integers must match bit for bit; floats may differ by the order of the fp32 additions
+        # when the shard picks a tile family that splits the reduction
+        res["shard_ok"] = 1.0 if (exact or (not integer and rel <= 2e-6)) else 0.0
+        del full_ins, full_out
+
+    if time_gather and world > 1 and not weak:
+        shard.gather_output(local_out, full)  # warm-up: communicator set-up, allocations
+        _barrier(world, dev)
+        g0 = torch.cuda.Event(enable_timing=True)
+        g1 = torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        gathered = shard.gather_output(local_out, full)
+        g1.record(stream)
+        torch.cuda.synchronize(dev)
+        res["gather_ms"] = g0.elapsed_time(g1)
+        res["gather_bytes"] = int(gathered.numel() * gathered.element_size())
+        del gathered
+
     if e2e_steps > 0:
+        torch.cuda.nvtx.range_push(f"bench:{name}:e2e")
         mod = runtime.Module(desc)
         pin_in = [torch.from_numpy(np.ascontiguousarray(x)).pin_memory() for x in host_local]
         pin_out = torch.empty(out_shape(desc), dtype=out_dtype).pin_memory()
         np_args = [t.numpy() for t in pin_in] + [pin_out.numpy()]
         for _ in range(2):
             mod(*np_args)
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
+        _barrier(world, dev)
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
@@ -362,6 +488,7 @@ def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_st
         res["h2d"] = int(sum(t.numel() * t.element_size() for t in pin_in))
         res["d2h"] = int(pin_out.numel() * pin_out.element_size())
         res["e2e_launches"] = e2e_steps * mod.launches_per_call
+        torch.cuda.nvtx.range_pop()
     del sets, calls
     torch.cuda.empty_cache()
     return res
@@ -400,38 +527,67 @@ class _Null:
 
 
 def reduce_over_ranks(res, world, dev):
-    """max of the times, sum of the work, over ranks."""
+    """max of the times, sum of the work, min of the parity flags, over ranks; plus every rank's
+    own end-to-end time (the ranks share the host's bus, so the aggregate alone hides who waits)."""
+    keys_max = ["ms", "burst_ms", "gather_ms", "shard_rel_l2"]
+    keys_sum = ["ops_local", "bytes_local", "launches", "h2d", "d2h"]
+    keys_min = ["shard_ok", "shard_bit_exact"]
+    out = {k: float(res.get(k) or 0.0) for k in keys_max + keys_sum + keys_min}
+    out["e2e_ms"] = res["e2e_ms"]
+    out["e2e_ms_per_rank"] = [res["e2e_ms"]] if res["e2e_ms"] else None
     if world == 1:
-        return res["ms"], res["e2e_ms"], res["ops_local"], res["bytes_local"], res["launches"], \
-            res["h2d"], res["d2h"]
+        return out
     import torch
     import torch.distributed as dist
-    t = torch.tensor([res["ms"], res["e2e_ms"] or 0.0], dtype=torch.float64, device=f"cuda:{dev}")
+    tdev = f"cuda:{dev}"
+    t = torch.tensor([out[k] for k in keys_max] + [res["e2e_ms"] or 0.0], dtype=torch.float64,
+                     device=tdev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    s = torch.tensor([res["ops_local"], res["bytes_local"], float(res["launches"]),
-                      float(res["h2d"]), float(res["d2h"])], dtype=torch.float64,
-                     device=f"cuda:{dev}")
-    dist.all_reduce(s, op=dist.ReduceOp.SUM)
-    return float(t[0]), (float(t[1]) or None), float(s[0]), float(s[1]), int(s[2]), int(s[3]), \
-        int(s[4])
+    for i, k in enumerate(keys_max):
+        out[k] = float(t[i])
+    out["e2e_ms"] = float(t[-1]) or None
+    u = torch.tensor([out[k] for k in keys_sum], dtype=torch.float64, device=tdev)
+    dist.all_reduce(u, op=dist.ReduceOp.SUM)
+    for i, k in enumerate(keys_sum):
+        out[k] = float(u[i])
+    v = torch.tensor([out[k] for k in keys_min], dtype=torch.float64, device=tdev)
+    dist.all_reduce(v, op=dist.ReduceOp.MIN)
+    for i, k in enumerate(keys_min):
+        out[k] = float(v[i])
+    mine = torch.tensor([res["e2e_ms"] or 0.0], dtype=torch.float64, device=tdev)
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    out["e2e_ms_per_rank"] = [float(x) for x in every] if out["e2e_ms"] else None
+    return out
 
 
-def roofline_for(desc_full, ops, byts, ms_per_step, n_gpus, peaks, peaks_kind, long_region):
+def roofline_for(desc_full, ops, byts, ms_per_step, n_gpus, peaks, peaks_kind, long_region,
+                 int8_peak=None):
+    """Roofline record of one timing.  Denominators: the measured bf16 tensor rate (fp16 runs at the
+    same rate; tf32 at half of it, stated), the int8 rate measured in this run with the vendor
+    library when available (else twice the bf16 rate, stated), the measured copy bandwidth; the
+    burst figures for short regions, the sustained ones for regions of half a second and more."""
     from amos_b200 import _lib
     i8 = desc_full.in_dtype == _lib.AMOSB_S8
-    tc_key = "bf16_tflops_sustained" if long_region else "bf16_tflops"
     tf32 = desc_full.in_dtype == _lib.AMOSB_F32
-    tc_peak = peaks[tc_key] * (NOMINAL_INT8_OVER_F16 if i8 else NOMINAL_TF32_OVER_F16 if tf32
-                               else 1.0) * n_gpus
+    tc_key = "bf16_tflops_sustained" if long_region else "bf16_tflops"
+    if i8 and int8_peak:
+        per_gpu = int8_peak["int8_tops_sustained" if long_region else "int8_tops"]
+        note = ("int8_tops_sustained" if long_region else "int8_tops") + \
+            " of measured (torch._int_mm 8192^3 in this run)"
+    else:
+        per_gpu = peaks[tc_key] * (NOMINAL_INT8_OVER_F16 if i8 else NOMINAL_TF32_OVER_F16 if tf32
+                                   else 1.0)
+        note = (f"{tc_key} of {peaks_kind}" + (" x2 (int8 rate assumed twice the measured bf16 "
+                                               "rate)" if i8 else "") +
+                (" x0.5 (tf32 rate assumed half the measured bf16 rate)" if tf32 else ""))
+    tc_peak = per_gpu * n_gpus
     hbm_peak = peaks["hbm_gbs"] * n_gpus
     ai = ops / byts
     ridge = tc_peak * 1e12 / (hbm_peak * 1e9)
     sec = ms_per_step / 1e3
     if ai >= ridge:
         achieved = ops / sec / 1e12
-        note = (f"{tc_key} of {peaks_kind}" + (" x2 (int8 rate assumed twice the measured bf16 "
-                                               "rate)" if i8 else "") +
-                (" x0.5 (tf32 rate assumed half the measured bf16 rate)" if tf32 else ""))
         return {"bound": "tensor", "achieved": achieved, "peak": tc_peak,
                 "unit": "TOP/s" if i8 else "TFLOP/s", "frac": achieved / tc_peak,
                 "traffic": None, "peak_source": note}
@@ -441,18 +597,19 @@ def roofline_for(desc_full, ops, byts, ms_per_step, n_gpus, peaks, peaks_kind, l
             "peak_source": f"hbm_gbs of {peaks_kind}"}
 
 
-# DRAM traffic per launch of the dominant kernel from the ncu captures summarised under
-# profiles/ (bytes read + written); None where no capture exists for the workload.
-NCU_TRAFFIC_BYTES = {
-    "gemm_f16_4096": 71.4e6 + 16.1e6,
-    "gemm_s8_8192": 305.4e6 + 237.6e6,
-    "bgemm_f16_96x512x512x64": 12.6e6 + 0.3e6,
-    "bgemm_f16_96x512x64x512": 56.7e6 + 0.2e6,
-    "conv_c3a_n256_c64_56x56_k256_1x1": 105.3e6 + 762.6e6,
-    "conv_c3b_n256_c128_28x28_k128_3x3": (51.7e6 + 11.8e6) + (51.7e6 + 48.6e6),
-    "conv_nhwc_c3b_n256_28x28_c128_k128_3x3": 51.7e6 + 46.7e6,
-    "conv_nhwc_c3c_n256_14x14_c256_k256_3x3": 26.9e6 + 2.7e6,
-}
+def config_for(name, world, scaling):
+    """The `config` object of the JSON line; both arms print the same one."""
+    w = WORKLOADS[name]
+    if world == 1:
+        sharding = "none"
+    elif scaling == "weak":
+        sharding = (f"{world} x the named configuration along rows of M / batch / images, one "
+                    f"named configuration per rank, no collective")
+    else:
+        sharding = (f"rows of M / batch / images of the named configuration split over {world} "
+                    f"ranks, B / filter replicated, no collective")
+    return {"workload": name, "shape": {k: v for k, v in w.items() if k not in ("seed", "shard")},
+            "sharding": sharding}
 
 
 def cpu_baseline(name, budget_s=12.0, threads=1, order=0):
@@ -483,6 +640,7 @@ def cpu_baseline(name, budget_s=12.0, threads=1, order=0):
         nimg = int(max(1, min(w["n"], budget_s / max(t1, 1e-6))))
         t = run(nimg) if nimg > 1 else t1
         ops = per_img * nimg
+        whole = nimg == w["n"]
         sample = f"{nimg} of {w['n']} images"
     else:
         a, b = host
@@ -501,11 +659,36 @@ def cpu_baseline(name, budget_s=12.0, threads=1, order=0):
         t = run(rows) if rows > probe else t1
         unit_ops = 2.0 * w["n"] * w["k"] * (1 if w["kind"] == "gemm" else w["m"])
         ops = unit_ops * rows
+        whole = rows == rows_total
         sample = f"{rows} of {rows_total} " + ("rows of M" if w["kind"] == "gemm" else "batches")
     i8 = w.get("dtype") == "s8"
+    how = "the whole workload" if whole else f"extrapolated from a slice: {sample}"
     return {"value": ops / t / 1e12, "unit": "TOP/s" if i8 else "TFLOP/s", "cores": threads,
-            "kind": "port", "sample": sample + f", {t:.1f} s, te_llvm arithmetic, loop order "
+            "kind": "port", "sample": how + f", {t:.1f} s, te_llvm arithmetic, loop order "
             + ("i,j,k as scheduled by default" if order == 0 else "interchanged")}
+
+
+def _line_for(name, args, world, res, red, peaks, peaks_kind, int8_peak):
+    """value / roofline / burst records of one measured workload (rank 0)."""
+    w = WORKLOADS[name]
+    full = make_desc(w)
+    i8 = w.get("dtype") == "s8"
+    steps_total = args.steps * res["passes"]
+    ms_per_step = red["ms"] / steps_total
+    burst_ms_per_step = red["burst_ms"] / args.steps
+    ops, byts = red["ops_local"], red["bytes_local"]
+    long_region = red["ms"] >= 500.0
+    roof = roofline_for(full, ops, byts, ms_per_step, world, peaks, peaks_kind, long_region,
+                        int8_peak)
+    traffic, source = ncu_traffic(name)
+    roof["traffic"] = traffic
+    roof["traffic_source"] = source
+    burst = roofline_for(full, ops, byts, burst_ms_per_step, world, peaks, peaks_kind, False,
+                         int8_peak)
+    burst_rec = {"value": ops / (burst_ms_per_step / 1e3) / 1e12, "ms_per_step": burst_ms_per_step,
+                 "timed_region_s": red["burst_ms"] / 1e3, "frac": burst["frac"],
+                 "peak": burst["peak"], "peak_source": burst["peak_source"]}
+    return ms_per_step, ops / (ms_per_step / 1e3) / 1e12, roof, burst_rec, i8
 
 
 def run_ours(args):
@@ -526,74 +709,112 @@ def run_ours(args):
     peaks, peaks_kind = load_peaks()
     name = args.workload
     w = WORKLOADS[name]
-    full = make_desc(w)
     sampler = ClockSampler(dev) if rank == 0 else None
+    need_i8 = w.get("dtype") == "s8" or not args.no_others
+    int8_peak = measure_int8_library_peak(dev) if need_i8 else None
+    if world > 1 and need_i8:
+        # every rank measured its own GPU; the slowest one is the job's denominator
+        import torch.distributed as dist
+        vals = torch.tensor([int8_peak["int8_tops"] if int8_peak else 0.0,
+                             int8_peak["int8_tops_sustained"] if int8_peak else 0.0],
+                            dtype=torch.float64, device=f"cuda:{dev}")
+        dist.all_reduce(vals, op=dist.ReduceOp.MIN)
+        if float(vals[0]) > 0 and int8_peak:
+            int8_peak["int8_tops"], int8_peak["int8_tops_sustained"] = float(vals[0]), float(vals[1])
+        else:
+            int8_peak = None
     res = measure_workload(name, args.steps, args.warmup, world, rank, dev, sampler,
-                           e2e_steps=max(3, min(args.steps, 20)), scaling=args.scaling)
-    ms, e2e_ms, ops, byts, launches, h2d, d2h = reduce_over_ranks(res, world, dev)
-    ms_per_step = ms / args.steps
-    i8 = w.get("dtype") == "s8"
+                           e2e_steps=max(3, min(args.steps, 20)), scaling=args.scaling,
+                           min_region_s=args.min_region_s, check_shard=True, time_gather=True)
+    red = reduce_over_ranks(res, world, dev)
+    ms_per_step, value, roof, burst_rec, i8 = _line_for(name, args, world, res, red, peaks,
+                                                        peaks_kind, int8_peak)
     unit = "TOP/s" if i8 else "TFLOP/s"
-    value = ops / (ms_per_step / 1e3) / 1e12
-    long_region = ms > 500.0
-    roof = roofline_for(full, ops, byts, ms_per_step, world, peaks, peaks_kind, long_region)
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name)
+    ops = red["ops_local"]
     e2e_steps = res.get("e2e_steps", 1)
-    e2e_val = ops / ((e2e_ms / e2e_steps) / 1e3) / 1e12 if e2e_ms else None
+    e2e_val = ops / ((red["e2e_ms"] / e2e_steps) / 1e3) / 1e12 if red["e2e_ms"] else None
 
-    # the other named configurations, briefly
+    weak_rec = None
+    if world > 1 and args.scaling == "strong" and w["shard"]:
+        wres = measure_workload(name, args.steps, 3, world, rank, dev, scaling="weak")
+        wred = reduce_over_ranks(wres, world, dev)
+        wms = wred["ms"] / args.steps
+        weak_rec = {"value": wred["ops_local"] / (wms / 1e3) / 1e12, "unit": unit,
+                    "ms_per_step": wms,
+                    "note": "every rank runs the named configuration on its own rows / batches / "
+                            "images (the job is n_gpus times the configuration); short region"}
+
+    # the other named configurations, briefly (short regions: burst denominators)
     others = {}
     if not args.no_others:
+        steps_o = max(5, min(args.steps, 30))
         for other in WORKLOADS:
             if other == name:
                 continue
-            r = measure_workload(other, max(5, min(args.steps, 30)), 3, world, rank, dev,
-                                 scaling=args.scaling)
+            r = measure_workload(other, steps_o, 3, world, rank, dev, scaling=args.scaling,
+                                 check_shard=True)
             if r is None:
                 continue
-            steps_o = max(5, min(args.steps, 30))
-            o_ms, _, o_ops, o_bytes, _, _, _ = reduce_over_ranks(r, world, dev)
+            o_red = reduce_over_ranks(r, world, dev)
             d_o = make_desc(WORKLOADS[other])
-            per = o_ms / steps_o
-            rf = roofline_for(d_o, o_ops, o_bytes, per, world, peaks, peaks_kind, False)
-            others[other] = {"value": o_ops / (per / 1e3) / 1e12,
+            per = o_red["ms"] / steps_o
+            rf = roofline_for(d_o, o_red["ops_local"], o_red["bytes_local"], per, world, peaks,
+                              peaks_kind, False, int8_peak)
+            others[other] = {"value": o_red["ops_local"] / (per / 1e3) / 1e12,
                              "unit": "TOP/s" if WORKLOADS[other].get("dtype") == "s8" else "TFLOP/s",
                              "us_per_step": per * 1e3, "roofline_bound": rf["bound"],
                              "roofline_frac": rf["frac"], "kernels_per_step": r["launches_per_step"]}
+            if world > 1:
+                others[other]["shard_parity"] = bool(o_red["shard_ok"])
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(name)
     if rank == 0:
+        clocks = sampler.summary() if sampler else None
+        if clocks and clocks.get("sm_mhz"):
+            clocks["ms_per_step_x_mhz"] = ms_per_step * clocks["sm_mhz"]
         line = {
             "metric": "TFLOP/s (int8: TOPS) per conv/GEMM config",
             "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None,
+            "scaling": args.scaling if world > 1 else "strong", "vs_baseline": None,
             "dtype": "s8" if i8 else ("tf32" if w.get("dtype") == "f32" else "f16"),
             "data": "synthetic",
-            "config": {"workload": name, "shape": {k: v for k, v in w.items()
-                                                   if k not in ("seed", "shard")},
-                       "sharding": ("none" if world == 1 else
-                                    (f"{world} x the named configuration along rows of M / batch / "
-                                     f"images, one named configuration per rank, no collective"
-                                     if args.scaling == "weak" else
-                                     f"rows of M / batch / images of the named configuration "
-                                     f"split over {world} ranks, no collective")),
-                       "launch": res.get("launch"), "rank0_cpus": numa,
-                       "l2": f"rotating {res.get('nsets', 1)} operand sets "
-                             f"({res.get('nsets', 1) * res['bytes_local'] / 1e6:.0f} MB per rank) "
-                             "larger than the 126 MB L2"},
-            "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h,
+            "config": config_for(name, world, args.scaling),
+            "run": {"launch": res.get("launch"), "rank0_cpus": numa,
+                    "passes": res["passes"], "timed_region_s": red["ms"] / 1e3,
+                    "l2": f"rotating {res.get('nsets', 1)} operand sets "
+                          f"({res.get('nsets', 1) * res['bytes_local'] / 1e6:.0f} MB per rank) "
+                          "larger than the 126 MB L2"},
+            "burst": burst_rec,
+            "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": int(red["h2d"]),
+                    "d2h_bytes_per_step": int(red["d2h"]),
+                    "ms_per_step_per_rank": ([x / e2e_steps for x in red["e2e_ms_per_rank"]]
+                                             if red["e2e_ms_per_rank"] else None),
                     "note": "Module(*numpy) -> amosb_run_host: pinned host operands copied in, "
-                            "kernels, full output copied back, every step"},
-            "gpu_launches": launches,
+                            "kernels, full output copied back, every step; all ranks share one "
+                            "host's PCIe and memory bus"},
+            "gpu_launches": int(red["launches"]),
             "roofline": roof,
+            "int8_peak": int8_peak,
             "cpu_baseline": cpu,
-            "clocks": sampler.summary() if sampler else None,
+            "clocks": clocks,
             "configs": others,
         }
+        if world > 1 and args.scaling == "strong":
+            line["shard_parity"] = bool(red["shard_ok"])
+            line["shard_parity_detail"] = {
+                "bit_exact": bool(red["shard_bit_exact"]), "max_rel_l2": red["shard_rel_l2"],
+                "how": "every rank runs the unsharded operator on its own GPU from the same seed "
+                       "and compares its shard with the same rows / batches / images"}
+            gbytes = res.get("gather_bytes", 0)
+            line["gather"] = {"ms": red["gather_ms"], "bytes": gbytes,
+                              "gbs": (gbytes / (red["gather_ms"] / 1e3) / 1e9
+                                      if red["gather_ms"] else None),
+                              "note": "shard.gather_output: NCCL all-gather of the output shards "
+                                      "to every rank, outside the timed compute path"}
+            line["weak_scaling"] = weak_rec
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
@@ -654,19 +875,21 @@ def run_reference(args):
     dt = time.perf_counter() - t
     value = per_unit * units * args.steps / dt / 1e12
     unit = "TOP/s" if i8 else "TFLOP/s"
-    sample = (f"{units} of {total_units} {unit_name} per step; C restatement of the te default "
-              f"schedule (loops i,j,k), te_llvm arithmetic, OpenMP over the outer axis")
+    how = "the whole workload" if units == total_units else \
+        f"extrapolated from a slice: {units} of {total_units} {unit_name} per step"
+    sample = (f"{how}; C restatement of the te default schedule (loops i,j,k), te_llvm "
+              f"arithmetic, OpenMP over the outer axis")
     print(json.dumps({
         "impl": "reference",
         "metric": "TFLOP/s (int8: TOPS) per conv/GEMM config",
         "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": args.scaling, "vs_baseline": None,
+        "scaling": args.scaling if args.gpus > 1 else "strong", "vs_baseline": None,
         "dtype": "s8" if i8 else ("tf32" if w.get("dtype") == "f32" else "f16"),
         "data": "synthetic",
-        "config": {"workload": name,
-                   "note": "the reference (TVM llvm build) cannot be built here; this is its CPU "
-                           "restatement (oracle port), host cores only"},
+        "config": config_for(name, args.gpus, args.scaling),
+        "note": "the reference (TVM llvm build) cannot be built here; this is its CPU restatement "
+                "(oracle port) on the host cores of rank 0; the figure does not depend on n_gpus",
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -681,10 +904,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="N > 1: weak = every rank runs the named configuration on its own rows / "
-                         "batches / images (the job is N times the configuration); strong = the "
-                         "named configuration is split over the ranks")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: strong = the named configuration is split over the ranks (rows of "
+                         "M / batches / images); weak = every rank runs the named configuration on "
+                         "its own rows / batches / images (the job is N times the configuration)")
+    ap.add_argument("--min-region-s", type=float, default=0.5,
+                    help="replay the captured steps until the timed region of the headline "
+                         "workload lasts at least this long (0: one pass)")
     ap.add_argument("--no-others", action="store_true", help="skip the non-headline configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

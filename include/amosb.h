@@ -52,7 +52,10 @@ typedef enum AmosbOpKind {
  * Tensor argument: the fields of a DLTensor that the generated host function of the reference
  * checks before launching (reference: src/tir/transforms/make_packed_api.cc:107-198,
  * src/tir/transforms/arg_binder.cc:150-299).  `strides` may be NULL (compact row-major) or must
- * describe a compact row-major tensor; `data + byte_offset` must be 16-byte aligned.
+ * describe a compact row-major tensor; `data + byte_offset` must be 16-byte aligned.  The struct has
+ * no device_type field: amosb_run takes device memory only and verifies that with the CUDA runtime
+ * (every pointer must be device or managed memory of `device_id`); amosb_packed_call below takes
+ * real DLTensors and checks their device_type as the reference does.
  */
 typedef struct AmosbTensor {
   void* data;
@@ -190,6 +193,87 @@ int amosb_describe_plan(const AmosbOpDesc* desc, int device, char* buf, int buf_
 #define AMOSB_STATIC_SCRATCH_BYTES (8ll * 1024 * 1024)
 int amosb_conv2d_nchw_static(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in,
                              AmosbTensor* outs, int n_out, void* cuda_stream);
+
+
+/*
+ * Synchronise `device` and turn a device-side wait that ran out into an error code: returns 0 when
+ * the status word is clear, else AMOSB_ERR_DEVICE_TIMEOUT (-4) with the wait's code (101..105) in
+ * the message, and clears the word.  The kernels bound every wait (2 s by default; the environment
+ * variable AMOSB_WAIT_BUDGET_NS overrides it for launches made afterwards) and give up instead of
+ * hanging; this is where the host learns of it.  Counterpart of the per-candidate time-outs and
+ * MeasureErrorNo codes of the reference's measurement loop
+ * (reference: python/tvm/auto_tensorize/search/measure.py:529-554, 755-785).
+ */
+int amosb_sync_check(int device);
+
+/*
+ * Stream that amosb_packed_call launches on, per calling thread and device (NULL = the default
+ * stream).  Counterpart of TVMSetStream (reference: include/tvm/runtime/c_runtime_api.h:476), which
+ * sets the thread-local stream the reference's CUDA module launches on
+ * (reference: src/runtime/cuda/cuda_module.cc:170).
+ */
+int amosb_set_stream(int device, void* cuda_stream);
+
+/*
+ * The reference's own calling convention.  A module built by the reference is entered through
+ *   int f(TVMValue* args, int* type_codes, int num_args, TVMValue* out_ret_value,
+ *         int* out_ret_tcode, void* resource_handle)
+ * (TVMBackendPackedCFunc, reference: include/tvm/runtime/c_backend_api.h:49-51) with one DLTensor*
+ * per argument.  The structs below restate the layout of the DLPack release the reference vendors
+ * (DLContext{device_type, device_id}, DLDataType{code, bits, lanes}; reference:
+ * include/tvm/runtime/c_runtime_api.h:79-135 for the type codes and the TVMValue union), under
+ * names of their own so that this header can be included next to dlpack.h.
+ */
+typedef struct AmosbDLContext {
+  int32_t device_type; /* AMOSB_DL_GPU is the only type accepted */
+  int32_t device_id;
+} AmosbDLContext;
+typedef struct AmosbDLDataType {
+  uint8_t code; /* AMOSB_DL_INT, AMOSB_DL_FLOAT, AMOSB_DL_BFLOAT */
+  uint8_t bits;
+  uint16_t lanes; /* must be 1 */
+} AmosbDLDataType;
+typedef struct AmosbDLTensor {
+  void* data;
+  AmosbDLContext ctx;
+  int32_t ndim;
+  AmosbDLDataType dtype;
+  int64_t* shape;
+  int64_t* strides; /* in elements, or NULL for compact row-major */
+  uint64_t byte_offset;
+} AmosbDLTensor;
+typedef union AmosbTVMValue {
+  int64_t v_int64;
+  double v_float64;
+  void* v_handle;
+  const char* v_str;
+  AmosbDLDataType v_type;
+  AmosbDLContext v_ctx;
+} AmosbTVMValue;
+
+#define AMOSB_DL_GPU 2            /* kDLGPU */
+#define AMOSB_DL_INT 0            /* kDLInt */
+#define AMOSB_DL_FLOAT 2          /* kDLFloat */
+#define AMOSB_DL_BFLOAT 4         /* kDLBfloat */
+#define AMOSB_TVM_NULLPTR 4       /* kTVMNullptr */
+#define AMOSB_TVM_DLTENSOR_HANDLE 7 /* kTVMDLTensorHandle */
+#define AMOSB_TVM_NDARRAY_HANDLE 13 /* kTVMNDArrayHandle */
+
+/*
+ * Run the operator described by `resource_handle` (a `const AmosbOpDesc*`) on `num_args` tensors:
+ * the inputs in the callable's order, then the output.  Performs the checks of the reference's
+ * generated prologue before anything is launched (reference: src/tir/transforms/make_packed_api.cc:
+ * 107-198, src/tir/transforms/arg_binder.cc:150-299): argument count, handle type codes, ndim,
+ * dtype code / bits / lanes, every shape extent, compact (or NULL) strides, byte_offset alignment,
+ * device_type == kDLGPU and one device_id for all tensors, which then becomes current.  Launches
+ * on the stream set with amosb_set_stream; the conv scratch, which the reference obtains with
+ * TVMBackendAllocWorkspace (reference: include/tvm/runtime/c_backend_api.h:87-100), comes from a
+ * buffer the library keeps per device and grows on demand.  Returns 0, or -1 with the message (which
+ * starts with this library's own code, "[amosb -2] ...") in amosb_last_error(), as the reference's
+ * convention asks.
+ */
+int amosb_packed_call(AmosbTVMValue* args, int* type_codes, int num_args,
+                      AmosbTVMValue* out_ret_value, int* out_ret_tcode, void* resource_handle);
 
 #ifdef __cplusplus
 }

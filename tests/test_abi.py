@@ -140,3 +140,76 @@ def test_no_cpu_path(built_lib):
     from amos_b200 import device
     with pytest.raises(_lib.AmosbError):
         device.tensor_arg(torch.zeros(4, 4, dtype=torch.float16))
+
+
+def test_dltensor_layout_is_the_reference_one(built_lib):
+    # data 0, ctx 8, ndim 16, dtype 20, shape 24, strides 32, byte_offset 40: 48 bytes
+    T = _lib.AmosbDLTensor
+    assert ctypes.sizeof(T) == 48 and ctypes.sizeof(_lib.AmosbTVMValue) == 8
+    assert [getattr(T, f).offset for f in ("data", "ctx", "ndim", "dtype", "shape", "strides",
+                                           "byte_offset")] == [0, 8, 16, 20, 24, 32, 40]
+
+
+def _dl(arr, code, **kw):
+    return _lib.make_dl_tensor(arr.ctypes.data, 0, code, list(arr.shape), **kw)
+
+
+def test_packed_call_checks_what_the_generated_prologue_checks(built_lib):
+    """The PackedFunc-shaped entry refuses, with -1 and a message that carries the library's own
+    code, everything the reference's generated host function asserts: argument count, handle type
+    codes, device_type, device_id, dtype code / bits / lanes, shapes, strides."""
+    d = _lib.gemm_desc(64, 32, 48)
+    a = np.zeros((64, 48), np.float16)
+    b = np.zeros((48, 32), np.float16)
+    c = np.zeros((64, 32), np.float32)
+    f16, f32 = _lib.AMOSB_F16, _lib.AMOSB_F32
+    ta, ka = _dl(a, f16)
+    tb, kb = _dl(b, f16)
+    tc, kc = _dl(c, f32)
+    assert _lib.packed_call(d, [ta, tb]) == -1
+    assert "num_args should be 3" in _lib.last_error() and "[amosb -1]" in _lib.last_error()
+    assert _lib.packed_call(d, [ta, tb, tc], [7, 0, 7]) == -1  # an int where a tensor is expected
+    assert "Expect arg[1] to be pointer" in _lib.last_error()
+    assert _lib.packed_call(d, [ta, None, tc]) == -1
+    assert "NULL tensor handle" in _lib.last_error()
+    cpu, _k = _dl(a, f16, device_type=1)  # kDLCPU
+    assert _lib.packed_call(d, [cpu, tb, tc]) == -1
+    assert "arg0.device_type" in _lib.last_error()
+    other, _k2 = _lib.make_dl_tensor(b.ctypes.data, 1, f16, list(b.shape))
+    assert _lib.packed_call(d, [ta, other, tc]) == -1
+    assert "arg1.device_id" in _lib.last_error()
+    lanes2, _k3 = _dl(a, f16, lanes=2)
+    assert _lib.packed_call(d, [lanes2, tb, tc]) == -1
+    assert "lanes 2" in _lib.last_error()
+    wrong, _k4 = _dl(np.zeros((64, 48), np.float32), f32)
+    assert _lib.packed_call(d, [wrong, tb, tc]) == -1
+    assert "arg0.dtype is expected to be float16" in _lib.last_error()
+    short, _k5 = _dl(np.zeros((64, 40), np.float16), f16)
+    assert _lib.packed_call(d, [short, tb, tc]) == -1
+    assert "arg0.shape[1]" in _lib.last_error()
+    strided, _k6 = _dl(a, f16, strides=[96, 2])
+    assert _lib.packed_call(d, [strided, tb, tc]) == -1
+    assert "compact" in _lib.last_error()
+    # both handle kinds are tensors
+    # both handle kinds are tensors: this call gets past the prologue and stops at the memory check
+    # (host arrays: -1 with a GPU, -3 without a driver to ask)
+    rc = _lib.packed_call(d, [ta, tb, tc], [7, 13, 13])
+    assert rc == -1 and ("[amosb -1]" in _lib.last_error() or "[amosb -3]" in _lib.last_error())
+    lib = _lib.load()
+    assert lib.amosb_set_stream(0, None) == 0 and lib.amosb_set_stream(99, None) == _lib.AMOSB_ERR_ARG
+
+
+def test_host_memory_is_refused_by_the_device_entry_points(built_lib):
+    """amosb_run and amosb_packed_call never hand a host pointer to the copy engine: with a GPU the
+    CUDA runtime says what the memory is (-1), without one the query itself fails (-3)."""
+    import torch
+    d = _lib.gemm_desc(64, 32, 48)
+    a = np.zeros((64, 48), np.float16)
+    b = np.zeros((48, 32), np.float16)
+    c = np.full((64, 32), 7.0, np.float32)
+    rc = _run(d, a, b, c, (_lib.AMOSB_F16, _lib.AMOSB_F16, _lib.AMOSB_F32))
+    if torch.cuda.is_available():
+        assert rc == _lib.AMOSB_ERR_ARG and "device_type is expected to be cuda" in _lib.last_error()
+    else:
+        assert rc == _lib.AMOSB_ERR_CUDA
+    assert (c == 7.0).all()

@@ -241,9 +241,9 @@ def test_recognise_conv_hwnc(built_lib, cfg):
     assert _lib.workspace_bytes(d) == 0
     text = _lib.describe_plan(d)
     assert "conv-hwnc" in text and "umma_pair" not in text
-    with pytest.raises(_lib.AmosbError):
-        from amos_b200 import shard
-        shard.local_desc(d, 2, 0)
+    from amos_b200 import shard
+    half, start, count = shard.local_desc(d, 2, 1)  # images are split; the layout stays HWNC
+    assert half.kind == _lib.OP_CONV2D_HWNC and (start, count) == (N // 2, N - N // 2)
 
 
 def test_recognise_fused_trailing_stages(built_lib):

@@ -53,13 +53,36 @@ def test_local_desc_and_views():
     assert ld.kind == _lib.OP_CONV2D_NHWC and ld.conv_n == 2
     assert ins[0].shape == (2, 14, 14, 64) and ins[1].shape == (3, 3, 64, 32)
     assert outs[0].shape == (2, 14, 14, 32) and np.shares_memory(outs[0], yh)
-    # HWNC: images are the third axis -- one rank takes the operator whole, more ranks are refused
+    # HWNC: images are the third axis -- a rank's share is a strided slice, handed over compact
     wd = _lib.conv2d_hwnc_desc(14, 14, 256, 64, 32, 3, 3, pad=1)
     ld, start, count = shard.local_desc(wd, 1, 0)
     assert (ld.kind, ld.conv_n, start, count) == (_lib.OP_CONV2D_HWNC, 256, 0, 256)
-    with pytest.raises(_lib.AmosbError) as e:
-        shard.local_desc(wd, 2, 0)
-    assert e.value.code == _lib.AMOSB_ERR_UNSUPPORTED
+    ld, start, count = shard.local_desc(wd, 2, 1)
+    assert (ld.kind, ld.conv_n, start, count) == (_lib.OP_CONV2D_HWNC, 128, 128, 128)
+    xw = np.arange(4 * 4 * 6 * 8, dtype=np.float16).reshape(4, 4, 6, 8)
+    fw = np.zeros((3, 3, 8, 16), np.float16)
+    yw = np.zeros((4, 4, 6, 16), np.float32)
+    sd = _lib.conv2d_hwnc_desc(4, 4, 6, 8, 16, 3, 3, pad=1)
+    ld, ins, outs = shard.shard_arrays(sd, [xw, fw], [yw], 3, 2)
+    assert ld.conv_n == 2 and ins[0].shape == (4, 4, 2, 8) and ins[0].flags["C_CONTIGUOUS"]
+    assert np.array_equal(ins[0], xw[:, :, 4:6]) and outs[0].shape == (4, 4, 2, 16)
+    # fused addends: a vector over N stays whole, a tensor of the output's shape is cut with it
+    gd = _lib.gemm_desc(64, 16, 8)
+    gd.epilogue, gd.arg_c, gd.addend_dtype = _lib.EPI_ADD_VECTOR, 2, _lib.AMOSB_F32
+    bias = np.zeros((16,), np.float32)
+    ld, ins, _ = shard.shard_arrays(gd, [np.zeros((64, 8), np.float16), np.zeros((8, 16), np.float16),
+                                         bias], [], 4, 1)
+    assert ins[0].shape == (16, 8) and ins[1].shape == (8, 16) and ins[2].shape == (16,)
+    gd.epilogue = _lib.EPI_ADD_FULL
+    full = np.zeros((64, 16), np.float32)
+    ld, ins, _ = shard.shard_arrays(gd, [np.zeros((64, 8), np.float16), np.zeros((8, 16), np.float16),
+                                         full], [], 4, 1)
+    assert ins[2].shape == (16, 16) and np.shares_memory(ins[2], full)
+    bgd = _lib.gemm_desc(32, 16, 8, batch=6)
+    bgd.epilogue, bgd.arg_c, bgd.addend_dtype = _lib.EPI_ADD_VECTOR, 2, _lib.AMOSB_F32
+    ld, ins, _ = shard.shard_arrays(bgd, [np.zeros((6, 32, 8), np.float16),
+                                          np.zeros((6, 8, 16), np.float16), bias], [], 3, 0)
+    assert ins[0].shape == (2, 32, 8) and ins[1].shape == (2, 8, 16) and ins[2].shape == (16,)
     # more ranks than units
     small = _lib.conv2d_desc(1, 64, 56, 56, 64, 3, 3, pad=1)
     assert shard.local_desc(small, 2, 1)[2] == 0
@@ -105,6 +128,25 @@ def _worker(rank, world, port, tmpdir):
         local = o.c_conv2d_nchw(np.ascontiguousarray(ins[0]), ins[1], 1, 1, 1, "te_llvm")
         gathered = shard.gather_output(torch.from_numpy(local), cd)
         assert np.array_equal(gathered.numpy(), o.c_conv2d_nchw(x, w, 1, 1, 1, "te_llvm"))
+        # a GEMM with a bias vector and one with a full-shape addend, 37 rows over 2 ranks
+        bias = rng.uniform(-1, 1, (16,)).astype(np.float32)
+        resid = rng.uniform(-1, 1, (37, 16)).astype(np.float32)
+        for bits, addend in ((_lib.EPI_ADD_VECTOR, bias), (_lib.EPI_ADD_FULL, resid)):
+            fd = _lib.gemm_desc(37, 16, 24)
+            fd.epilogue, fd.arg_c, fd.addend_dtype = bits | _lib.EPI_RELU, 2, _lib.AMOSB_F32
+            ld, ins, _ = shard.shard_arrays(fd, [a, b, addend], [], world, rank)
+            local = np.maximum(o.c_gemm(np.ascontiguousarray(ins[0]), ins[1], "te_llvm") + ins[2], 0)
+            gathered = shard.gather_output(torch.from_numpy(local.astype(np.float32)), fd)
+            assert np.array_equal(gathered.numpy(),
+                                  np.maximum(ref + addend, 0).astype(np.float32))
+        # HWNC: the image axis is the third one; the gather puts the shards back in place
+        xw = rng.uniform(-1, 1, (5, 5, 3, 8)).astype(np.float16)
+        ww = rng.normal(0, 0.05, (3, 3, 8, 8)).astype(np.float16)
+        wd = _lib.conv2d_hwnc_desc(5, 5, 3, 8, 8, 3, 3, pad=1)
+        ld, ins, _ = shard.shard_arrays(wd, [xw, ww], [], world, rank)
+        local = o.c_conv2d_hwnc(ins[0], ins[1], 1, 1, 1, "te_llvm")
+        gathered = shard.gather_output(torch.from_numpy(local), wd)
+        assert np.array_equal(gathered.numpy(), o.c_conv2d_hwnc(xw, ww, 1, 1, 1, "te_llvm"))
         # max-over-ranks reduction used for timing
         t = torch.tensor([float(rank + 1)])
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
