@@ -10,7 +10,8 @@ import os
 from typing import Sequence
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libamosb.so")
+# AMOSB_LIBRARY overrides the path (e.g. a diagnostic build of the same sources)
+LIB_PATH = os.environ.get("AMOSB_LIBRARY") or os.path.join(HERE, "libamosb.so")
 
 AMOSB_OK = 0
 AMOSB_ERR_ARG = -1
@@ -108,6 +109,7 @@ _SIGNATURES = {
     "amosb_last_error": (ctypes.c_char_p, []),
     "amosb_recognize": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(AmosbOpDesc)]),
     "amosb_workspace_bytes": (ctypes.c_int64, [ctypes.POINTER(AmosbOpDesc)]),
+    "amosb_workspace_bytes_min": (ctypes.c_int64, [ctypes.POINTER(AmosbOpDesc)]),
     "amosb_run": (ctypes.c_int, [ctypes.POINTER(AmosbOpDesc), ctypes.POINTER(AmosbTensor),
                                  ctypes.c_int, ctypes.POINTER(AmosbTensor), ctypes.c_int,
                                  ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]),
@@ -259,6 +261,11 @@ def recognize(te_dag_text: str) -> AmosbOpDesc:
 
 def workspace_bytes(desc: AmosbOpDesc) -> int:
     return check(load().amosb_workspace_bytes(ctypes.byref(desc)))
+
+
+def workspace_bytes_min(desc: AmosbOpDesc) -> int:
+    """The part of `workspace_bytes` the call cannot do without (the rest only buys speed)."""
+    return check(load().amosb_workspace_bytes_min(ctypes.byref(desc)))
 
 
 def describe_plan(desc: AmosbOpDesc, device: int = -1) -> str:

@@ -287,13 +287,23 @@ int64_t amosb_workspace_bytes(const AmosbOpDesc* desc) {
     long long act, flt;
     int c8, c64;
     conv_workspace_layout(*desc, &act, &flt, &c8, &c64);
-    return act + flt;
+    return act + flt + tail_workspace_bytes(*desc);
   }
   if (desc->kind == AMOSB_OP_GEMM || desc->kind == AMOSB_OP_BATCHED_GEMM ||
       desc->kind == AMOSB_OP_CONV2D_NHWC || desc->kind == AMOSB_OP_CONV2D_HWNC)
-    return 0;
+    return tail_workspace_bytes(*desc);
   set_error("descriptor has no operator kind (%d)", desc->kind);
   return AMOSB_ERR_ARG;
+}
+
+int64_t amosb_workspace_bytes_min(const AmosbOpDesc* desc) {
+  if (desc == nullptr) {
+    set_error("NULL descriptor");
+    return AMOSB_ERR_ARG;
+  }
+  const int64_t all = amosb_workspace_bytes(desc);
+  if (all < 0) return all;
+  return all - tail_workspace_bytes(*desc);
 }
 
 int amosb_run(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in, AmosbTensor* outs,
@@ -313,14 +323,14 @@ int amosb_run(const AmosbOpDesc* desc, const AmosbTensor* ins, int n_in, AmosbTe
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (desc->kind == AMOSB_OP_CONV2D_NHWC || desc->kind == AMOSB_OP_CONV2D_HWNC) {
     return run_conv2d_nhwc(*desc, tensor_ptr(*A), tensor_ptr(*B), addend, tensor_ptr(outs[0]),
-                           device, stream);
+                           workspace, workspace_bytes, device, stream);
   }
   if (desc->kind == AMOSB_OP_CONV2D_NCHW) {
     return run_conv2d(*desc, tensor_ptr(*A), tensor_ptr(*B), addend, tensor_ptr(outs[0]),
                       workspace, workspace_bytes, device, stream);
   }
-  return run_gemm(*desc, tensor_ptr(*A), tensor_ptr(*B), addend, tensor_ptr(outs[0]), device,
-                  stream);
+  return run_gemm(*desc, tensor_ptr(*A), tensor_ptr(*B), addend, tensor_ptr(outs[0]), workspace,
+                  workspace_bytes, device, stream);
 }
 
 // Device buffers of the host-buffer path, kept per device and grown on demand so that repeated
@@ -711,6 +721,19 @@ int amosb_describe_plan(const AmosbOpDesc* desc, int device, char* buf, int buf_
                  "epilogue, %lld tiles on %lld %s",
                  dtype_name(desc->in_dtype), dtype_name(desc->out_dtype), fam, bn, rows, bn, stages,
                  tiles, tiles < slots ? tiles : slots, pair ? "CTA pairs" : "CTAs");
+  } else if (desc->kind == AMOSB_OP_CONV2D_NCHW && conv_is_pointwise_inplace(*desc)) {
+    const long long m = desc->conv_n * desc->conv_p * desc->conv_q;
+    const int pbn = pointwise_inplace_tile_n(*desc);
+    const long long tiles = ((m + 127) / 128) * ((desc->conv_k + pbn - 1) / pbn);
+    n = snprintf(buf, buf_len,
+                 "plan conv2d_nchw (1x1, stride 1, no padding, planes of %lld pixels: not a 16-byte "
+                 "multiple) %s->%s, operands in place (no re-layout, no workspace): [1] "
+                 "umma_persistent<%s,BN=%d,conv-1x1-inplace> tile 128x%dx64, %d smem stages, "
+                 "activation as MN-major A copied by four warps with 8-byte cp.async into the "
+                 "swizzled stage layout, filter as K-major TMA B, NCHW stores, %lld tiles on %lld CTAs",
+                 (long long)(desc->conv_p * desc->conv_q), dtype_name(desc->in_dtype),
+                 dtype_name(desc->out_dtype), ck, pbn, pbn, pbn == 256 ? 4 : (pbn == 128 ? 6 : 8),
+                 tiles, tiles < sms ? tiles : (long long)sms);
   } else if (desc->kind == AMOSB_OP_CONV2D_NCHW) {
     const long long m = desc->conv_n * desc->conv_p * desc->conv_q;
     const long long tiles = ((m + rows - 1) / rows) * ((desc->conv_k + bn - 1) / bn);

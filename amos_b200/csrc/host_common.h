@@ -32,17 +32,22 @@ const char* last_error();
 
 // launch.cu
 int run_gemm(const AmosbOpDesc& d, const void* a, const void* b, const void* addend, void* c,
-             int device, cudaStream_t stream);
+             void* workspace, long long workspace_bytes, int device, cudaStream_t stream);
 int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const void* addend, void* out,
                void* workspace, long long workspace_bytes, int device, cudaStream_t stream);
 int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, const void* addend,
-                    void* out, int device, cudaStream_t stream);
+                    void* out, void* workspace, long long workspace_bytes, int device,
+                    cudaStream_t stream);
+// scratch the shared-out tail of `d`'s schedule wants on a full B200 (0: the tail is not shared out)
+long long tail_workspace_bytes(const AmosbOpDesc& d);
 void conv_workspace_layout(const AmosbOpDesc& d, long long* act_bytes, long long* flt_bytes,
                            int* c_pad8, int* c_pad64);
 int choose_tile_n(const AmosbOpDesc& d, int sm_count);
 int choose_tile_rows(const AmosbOpDesc& d, int sm_count);  // 128, or 256 for pairs and tall tiles
 bool choose_cta_pairs(const AmosbOpDesc& d, int sm_count);
 bool conv_is_pointwise_gemm(const AmosbOpDesc& d);
+bool conv_is_pointwise_inplace(const AmosbOpDesc& d);
+int pointwise_inplace_tile_n(const AmosbOpDesc& d);
 int status_peek(int device, int clear);
 int* device_status_ptr(int device);  // device address of the status word, or nullptr
 int device_sm_count(int device);

@@ -63,6 +63,13 @@ static int load_driver_entry_points() {
 // Per-device state
 // --------------------------------------------------------------------------------------------
 __device__ int g_status_word = 0;
+// Flags of the shared-out tail (one word per CTA and epilogue warp; see UmmaParams::sk_flags).
+// They are zero when the library is loaded, and the kernels leave them zero (the CTA that reads a
+// flag clears it).  A launch takes the next of kSkSlots blocks, so that kernels running side by
+// side on different streams do not share a block unless 64 such launches are in flight at once.
+constexpr int kSkSlots = 64;
+constexpr int kSkCtasMax = 160;
+__device__ unsigned int g_sk_flags[kSkSlots * kSkCtasMax * 4];
 #ifdef AMOSB_ROLE_CYCLES
 // Diagnostic build only (-DAMOSB_ROLE_CYCLES): cycles each role of the single-CTA kernel spent
 // waiting and in total, summed over CTAs; read and cleared by amosb_debug_role_cycles().
@@ -80,7 +87,9 @@ struct DeviceState {
   int sm_count = 0;
   int cc_major = 0, cc_minor = 0;
   int* status_ptr = nullptr;
+  unsigned int* sk_flags = nullptr;
 };
+static std::atomic<unsigned int> g_sk_next[64];
 static DeviceState g_dev[64];
 static std::mutex g_dev_mutex;
 
@@ -106,6 +115,9 @@ static int get_device_state(int device, DeviceState** out) {
     void* p = nullptr;
     AMOSB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_status_word));
     st.status_ptr = static_cast<int*>(p);
+    p = nullptr;
+    AMOSB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_sk_flags));
+    st.sk_flags = static_cast<unsigned int*>(p);
     st.init = true;
   }
   *out = &st;
@@ -444,7 +456,7 @@ static int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   AMOSB_CUDA_CHECK(cudaGetSymbolAddress(&rc_ptr, g_role_cycles));
   pd.role_cycles = static_cast<unsigned long long*>(rc_ptr);
   pd.dbg_skip = getenv("AMOSB_DBG_SKIP") ? atoi(getenv("AMOSB_DBG_SKIP")) : 0;
-  kernel<<<grid, kNumThreads, smem, stream>>>(tmA, tmB, tmC, pd);
+  kernel<<<grid, umma_threads(MODE), smem, stream>>>(tmA, tmB, tmC, pd);
 #else
   {
     // programmatic dependent of whatever precedes it in the stream (the re-layout kernel of an NCHW
@@ -453,7 +465,7 @@ static int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.blockDim = dim3(umma_threads(MODE), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -606,6 +618,48 @@ static int dispatch_pair_gemm(bool trans_b, bool epi_tma, int bn, const CUtensor
   return dispatch_pair_bn<KIND, true, kModeGemm, OutT, false>(bn, tmA, tmB, tmC, p, pairs, stream);
 }
 
+struct TailPlan {
+  int sk_tiles = 0, q = 0, r = 0;
+};
+// `tiles` tiles of `num_kb` k-blocks on `workers` CTAs (CTA pairs); a k-block of this tile family
+// takes about `kb_ns` nanoseconds.  Whole tiles cost ceil(tiles / workers) rounds of num_kb
+// k-blocks; when the last round is short, its k-blocks can be shared out evenly instead, at the
+// price of exchanging partial sums through L2.  The CTA that finishes a shared tile pulls each
+// other part's 128 KB with 128 threads, 16 KB in flight at a time: ~6 us per part (measured), which
+// only stays off the critical path when a round of whole tiles follows the shares (the exchange
+// then runs under that round's main loop) and the tile is not store-bound already.  So the tail
+// is shared out only where the gain is large and clear: a whole round follows, the shares save at
+// least half a round and at least 16 us.  (Measured on B200: 7x7 C512->K512 3x3 batch 256, NHWC
+// 53 -> 46 us; tf32 4096^3 214 -> 205 us.  The fp16 4096^3 GEMM, power-bound, and the 28x28 /
+// 14x14 3x3 layers, store-bound or with little to save, lose 2-16 us and are left alone.)
+// AMOSB_TAIL_SHARING=1 shares out whenever the last round is short (tests use it on small shapes),
+// AMOSB_NO_TAIL_SHARING=1 never does.
+static TailPlan plan_tail(long long tiles, int workers, int num_kb, double kb_ns) {
+  TailPlan t;
+  if (getenv("AMOSB_NO_TAIL_SHARING") != nullptr || workers <= 1 || num_kb < 2) return t;
+  const long long rem = tiles % workers;
+  if (rem == 0) return t;
+  const long long units = rem * num_kb;
+  const long long q = units / workers;
+  const char* force = getenv("AMOSB_TAIL_SHARING");
+  if (force != nullptr && force[0] == '1') {
+    if (q < 1) return t;
+  } else {
+    const long long saved_kb = num_kb - (units + workers - 1) / workers;
+    if (tiles < workers || q < 4 || saved_kb * 2 < num_kb || saved_kb * kb_ns < 16000.0) return t;
+  }
+  t.sk_tiles = static_cast<int>(rem);
+  t.q = static_cast<int>(q);
+  t.r = static_cast<int>(units % workers);
+  return t;
+}
+// Nanoseconds per k-block of a tile family (the constants of choose_plan).
+static double kb_cost_ns(int bn, int mt, bool pairs) {
+  if (pairs) return bn == 256 ? 410.0 : 335.0;
+  if (mt == 2) return 415.0;
+  return bn == 256 ? 400.0 : bn == 128 ? 240.0 : 168.0;
+}
+
 // Tile width and kernel family for a problem, from a small cost model: time ~ waves x cost of one
 // k-block of the tile.  The costs are nanoseconds per k-block and wave, fitted on B200 to GEMMs
 // with M = 256..4096, N = K = 4096 and to the batch-256 3x3 convolution layers: CTA pair x256:
@@ -658,10 +712,18 @@ void choose_plan(bool i8_mn, bool tall_ok, long long batch, long long m, long lo
     const long long slots = c.pair ? sm_count / 2 : sm_count;
     double waves = static_cast<double>((tiles + slots - 1) / slots);
     const long long rem = tiles % slots;
+    // a short last round whose k-blocks are shared out among all workers costs its share of a
+    // round plus the exchange of partial sums (see plan_tail)
+    const bool shared_tail =
+        plan_tail(tiles, static_cast<int>(slots), static_cast<int>(kblocks), c.cost).sk_tiles > 0;
+    if (shared_tail)
+      waves = static_cast<double>(tiles / slots) +
+              static_cast<double>((rem * kblocks + slots - 1) / slots + 3) / static_cast<double>(kblocks);
     // a short last wave of a pair launch costs less than its tile time: the idle SMs leave their
     // share of the power budget to the busy ones (seen from the third wave on; with two waves the
     // 7x7 layers of 512 channels measured 8 % faster on 128-wide single-CTA tiles)
-    if (c.pair && c.bn == 256 && tiles > 2 * slots && rem > 0 && 2 * rem <= slots) waves -= 0.25;
+    if (!shared_tail && c.pair && c.bn == 256 && tiles > 2 * slots && rem > 0 && 2 * rem <= slots)
+      waves -= 0.25;
     double cost = c.cost;
     // Over several waves a 256-wide pair tile is a little cheaper than the single-CTA tile (half
     // the B reads per SM leave more of the power budget to the tensor pipe); within one wave the
@@ -735,6 +797,52 @@ bool choose_cta_pairs(const AmosbOpDesc& d, int sm_count) {
 }
 
 // --------------------------------------------------------------------------------------------
+// Schedule: whole tiles round-robin, plus a shared-out tail where the last round would be short
+// --------------------------------------------------------------------------------------------
+// Completes the schedule fields of `p` (num_tiles and num_kb are final) and returns the number of
+// workers to launch.  The tail is shared out only if `ws` has room for one partial accumulator tile
+// per CTA (`partial_elems` 32-bit words each, `ctas_per_worker` CTAs per worker).
+static int setup_schedule(UmmaParams* p, DeviceState* st, int device, int workers_max,
+                          int ctas_per_worker, size_t partial_elems, void* ws, long long ws_bytes) {
+  // k-block time of the tile family, from the accumulator columns a CTA holds (a tall 256 x 128
+  // tile counts as 256 columns: the same MMA time per k-block)
+  const double kb_ns = kb_cost_ns(static_cast<int>(partial_elems / kBlockM), 1, ctas_per_worker == 2);
+  p->sk_tiles = 0;
+  p->sk_first = p->num_tiles;
+  p->sk_q = p->sk_r = 0;
+  p->sk_partials = nullptr;
+  p->sk_flags = st->sk_flags;
+  const TailPlan t = plan_tail(p->num_tiles, workers_max, p->num_kb, kb_ns);
+  const long long need =
+      static_cast<long long>(workers_max) * ctas_per_worker * partial_elems * 4;
+  if (t.sk_tiles > 0 && ws != nullptr && ws_bytes >= need &&
+      workers_max * ctas_per_worker <= kSkCtasMax &&
+      (reinterpret_cast<uintptr_t>(ws) & 15u) == 0) {
+    p->sk_tiles = t.sk_tiles;
+    p->sk_first = p->num_tiles - t.sk_tiles;
+    p->sk_q = t.q;
+    p->sk_r = t.r;
+    p->sk_partials = static_cast<uint32_t*>(ws);
+    const unsigned int slot = g_sk_next[device].fetch_add(1u) % kSkSlots;
+    p->sk_flags = st->sk_flags + static_cast<size_t>(slot) * kSkCtasMax * 4;
+    return workers_max;  // every worker has a share
+  }
+  return p->num_tiles < workers_max ? p->num_tiles : workers_max;
+}
+
+// Scratch the shared-out tail wants for `tiles` tiles on a full B200 (148 SMs), 0 if the tail is
+// not shared out.
+static long long tail_scratch_bytes(long long tiles, int num_kb, bool pairs, int mt, int bn) {
+  const int sms = 148;
+  const int workers = pairs ? sms / 2 : sms;
+  if (tiles > 0x7fffffffLL ||
+      plan_tail(tiles, workers, num_kb, kb_cost_ns(pairs ? bn : mt * bn, 1, pairs)).sk_tiles == 0)
+    return 0;
+  const long long elems = static_cast<long long>(pairs ? 1 : mt) * kBlockM * bn;
+  return static_cast<long long>(sms) * elems * 4;
+}
+
+// --------------------------------------------------------------------------------------------
 // GEMM family
 // --------------------------------------------------------------------------------------------
 // Core of the GEMM family: C[b] (M x N) = A[b or shared] (M x K, K-major) * B[b] (K x N row-major,
@@ -798,7 +906,8 @@ static CUtensorMapDataType tma_dtype_for(int in_dtype) {
 static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool trans_a, bool trans_b,
                          bool a_shared, long long batch, long long M, long long N, long long K,
                          int tile_n, int pair_mode, const TrailingOps& ops, const void* a,
-                         const void* b, void* c, cudaStream_t stream) {
+                         const void* b, void* c, void* ws, long long ws_bytes, int device,
+                         cudaStream_t stream) {
   const bool is_i8 = in_dtype == AMOSB_S8;
   const bool is_tf32 = in_dtype == AMOSB_F32;  // float32 operands, read by the MMA as tf32
   if (in_dtype == AMOSB_BF16 && out_dtype != AMOSB_F32) {
@@ -910,7 +1019,6 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
   p.epi_flags = ops.flags;
   p.addend_f16 = ops.f16;
   p.addend = ops.addend;
-  const int grid = (int)(tiles < st->sm_count ? tiles : st->sm_count);
   if (is_i8 && out_dtype != AMOSB_S32) {
     set_error("int8 GEMM writes int32");
     return AMOSB_ERR_UNSUPPORTED;
@@ -918,7 +1026,8 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
   if (pairs) {
     p.tiles_m = (int)((M + 2 * kBlockM - 1) / (2 * kBlockM));
     p.num_tiles = (int)tiles_pair;
-    const int npairs = (int)(tiles_pair < st->sm_count / 2 ? tiles_pair : st->sm_count / 2);
+    const int npairs = setup_schedule(&p, st, device, st->sm_count / 2, 2,
+                                      static_cast<size_t>(kBlockM) * bn, ws, ws_bytes);
     if (is_i8)
       return dispatch_pair_gemm<1, int32_t>(trans_b, epi_tma, bn, tmA, tmB, tmC, p, npairs, stream);
     if (out_dtype == AMOSB_F32)
@@ -929,6 +1038,8 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
     return AMOSB_ERR_UNSUPPORTED;
   }
 
+  const int grid = setup_schedule(&p, st, device, st->sm_count, 1,
+                                  static_cast<size_t>(mt) * kBlockM * bn, ws, ws_bytes);
   if (is_i8) {
     return dispatch_gemm<1, int32_t>(trans_a, trans_b, epi_tma, bn, tmA, tmB, tmC, p, grid, stream);
   }
@@ -944,7 +1055,7 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
 }
 
 int run_gemm(const AmosbOpDesc& d, const void* a, const void* b, const void* addend, void* c,
-             int device, cudaStream_t stream) {
+             void* workspace, long long workspace_bytes, int device, cudaStream_t stream) {
   DeviceState* st = nullptr;
   int rc = get_device_state(device, &st);
   if (rc != AMOSB_OK) return rc;
@@ -954,7 +1065,8 @@ int run_gemm(const AmosbOpDesc& d, const void* a, const void* b, const void* add
   rc = trailing_ops_for(d, addend, false, &ops);
   if (rc != AMOSB_OK) return rc;
   return run_gemm_core(st, d.in_dtype, d.out_dtype, d.trans_a != 0, d.trans_b != 0, false,
-                       d.batch, d.m, d.n, d.k, d.tile_n, d.cta_pair, ops, a, b, c, stream);
+                       d.batch, d.m, d.n, d.k, d.tile_n, d.cta_pair, ops, a, b, c, workspace,
+                       workspace_bytes, device, stream);
 }
 
 // --------------------------------------------------------------------------------------------
@@ -973,19 +1085,139 @@ bool conv_is_pointwise_gemm(const AmosbOpDesc& d) {
          d.conv_c % 8 == 0 && getenv("AMOSB_CONV_NO_POINTWISE") == nullptr;
 }
 
+// The other 1x1 / stride 1 / unpadded layers with 16-bit tensors whose planes are a multiple of 4
+// pixels (8 bytes) but not of 8: no tensor map can describe the activation, so it is brought into
+// shared memory by cp.async instead (kModeConvPw); the filter and the output need nothing special.
+bool conv_is_pointwise_inplace(const AmosbOpDesc& d) {
+  return d.kind == AMOSB_OP_CONV2D_NCHW && conv_elem_bytes(d) == 2 && d.conv_r == 1 &&
+         d.conv_s == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_h == 0 && d.pad_w == 0 &&
+         (d.conv_h * d.conv_w) % 4 == 0 && d.conv_c % 8 == 0 && !conv_is_pointwise_gemm(d) &&
+         d.cta_pair != 2 && d.cta_pair != 3 &&  // pinned pair / tall tiles: the re-layout path has them
+         getenv("AMOSB_CONV_NO_POINTWISE") == nullptr;
+}
+
 void conv_workspace_layout(const AmosbOpDesc& d, long long* act_bytes, long long* flt_bytes,
                            int* c_pad8, int* c_pad64) {
   // channels per pixel padded to 16 bytes, channels per filter tap to whole 128-byte k-blocks
   const int es = conv_elem_bytes(d);
   *c_pad8 = (int)round_up(d.conv_c, 16 / es);
   *c_pad64 = (int)round_up(d.conv_c, 128 / es);
-  if (conv_is_pointwise_gemm(d)) {
+  if (conv_is_pointwise_gemm(d) || conv_is_pointwise_inplace(d)) {
     *act_bytes = 0;
     *flt_bytes = 0;
     return;
   }
   *act_bytes = round_up(d.conv_n * d.conv_h * d.conv_w * (long long)(*c_pad8) * es, 1024);
   *flt_bytes = round_up(d.conv_k * d.conv_r * d.conv_s * (long long)(*c_pad64) * es, 1024);
+}
+
+// Tile width of the in-place 1x1 kernel: the narrowest of 64 / 128 / 256 that covers K_out, so that
+// the activation passes through the copying warps once (measured on the 14x14, C1024 -> K256 layer:
+// 128-wide tiles copy it twice and take 1.6x as long).
+int pointwise_inplace_tile_n(const AmosbOpDesc& d) {
+  if (d.tile_n == 64 || d.tile_n == 128 || d.tile_n == 256) return d.tile_n;
+  return d.conv_k > 128 ? 256 : d.conv_k > 64 ? 128 : 64;
+}
+
+static int run_conv2d_pointwise_inplace(DeviceState* st, const AmosbOpDesc& d, const void* act,
+                                        const void* flt, const void* addend, void* out, void* ws,
+                                        long long ws_bytes, int device, cudaStream_t stream) {
+  const long long PQ = d.conv_p * d.conv_q, Mtot = d.conv_n * PQ, C = d.conv_c, Kout = d.conv_k;
+  if (Mtot > 0x7fffffffLL || C * PQ * d.conv_n > (1LL << 40)) {
+    set_error("conv2d problem too large");
+    return AMOSB_ERR_UNSUPPORTED;
+  }
+  const int bn = pointwise_inplace_tile_n(d);
+  CUtensorMap tmA, tmB, tmC;
+  memset(&tmA, 0, sizeof(tmA));
+  memset(&tmC, 0, sizeof(tmC));
+  int rc = encode_tiled_2d(&tmB, tma_dtype_for(d.in_dtype), const_cast<void*>(flt), C, Kout, C * 2,
+                           64, bn);
+  if (rc != AMOSB_OK) return rc;
+  UmmaParams p;
+  memset(&p, 0, sizeof(p));
+  set_wait_params(&p);
+  p.M = (int)Mtot;
+  p.N = (int)Kout;
+  p.K = (int)C;
+  p.batch = 1;
+  p.mt = 1;
+  p.idesc_formats = idesc_formats_for(d.in_dtype);
+  p.tiles_m = (int)((Mtot + kBlockM - 1) / kBlockM);
+  p.tiles_n = (int)((Kout + bn - 1) / bn);
+  p.group_m = 16;
+  p.num_kb = (int)((C + 63) / 64);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.out = out;
+  p.status = st->status_ptr;
+  p.P = (int)d.conv_p;
+  p.Q = (int)d.conv_q;
+  p.PQ = (int)PQ;
+  p.conv_C = (int)C;
+  p.producers = 1;
+  p.act = act;
+  TrailingOps ops;
+  rc = trailing_ops_for(d, addend, false, &ops);
+  if (rc != AMOSB_OK) return rc;
+  p.epi_flags = ops.flags;
+  p.addend_f16 = ops.f16;
+  p.addend = ops.addend;
+  const int grid = setup_schedule(&p, st, device, st->sm_count, 1,
+                                  static_cast<size_t>(kBlockM) * bn, ws, ws_bytes);
+  const bool f32 = d.out_dtype == AMOSB_F32;
+  if (!f32 && d.out_dtype != AMOSB_F16) {
+    set_error("conv2d writes float32 or float16");
+    return AMOSB_ERR_UNSUPPORTED;
+  }
+  switch (bn) {
+    case 256:
+      return f32 ? launch_umma<0, 256, false, kModeConvPw, float, false, 1, true>(tmA, tmB, tmC, p, grid, stream)
+                 : launch_umma<0, 256, false, kModeConvPw, __half, false, 1, true>(tmA, tmB, tmC, p, grid, stream);
+    case 128:
+      return f32 ? launch_umma<0, 128, false, kModeConvPw, float, false, 1, true>(tmA, tmB, tmC, p, grid, stream)
+                 : launch_umma<0, 128, false, kModeConvPw, __half, false, 1, true>(tmA, tmB, tmC, p, grid, stream);
+    default:
+      return f32 ? launch_umma<0, 64, false, kModeConvPw, float, false, 1, true>(tmA, tmB, tmC, p, grid, stream)
+                 : launch_umma<0, 64, false, kModeConvPw, __half, false, 1, true>(tmA, tmB, tmC, p, grid, stream);
+  }
+}
+
+long long tail_workspace_bytes(const AmosbOpDesc& d) {
+  const int sms = 148;
+  const bool conv = d.kind == AMOSB_OP_CONV2D_NCHW || d.kind == AMOSB_OP_CONV2D_NHWC ||
+                    d.kind == AMOSB_OP_CONV2D_HWNC;
+  if (conv && (d.conv_n <= 0 || d.conv_c <= 0 || d.conv_k <= 0 || d.conv_p <= 0 || d.conv_q <= 0 ||
+               d.conv_r <= 0 || d.conv_s <= 0))
+    return 0;
+  if (!conv && (d.m <= 0 || d.n <= 0 || d.k <= 0 || d.batch <= 0)) return 0;
+  if (d.kind == AMOSB_OP_CONV2D_NCHW && conv_is_pointwise_inplace(d)) {
+    const int bn = pointwise_inplace_tile_n(d);
+    const long long m = d.conv_n * d.conv_p * d.conv_q;
+    const long long tiles = ((m + kBlockM - 1) / kBlockM) * ((d.conv_k + bn - 1) / bn);
+    return tail_scratch_bytes(tiles, (int)((d.conv_c + 63) / 64), false, 1, bn);
+  }
+  int bn = 0, mt = 1;
+  bool pairs = false;
+  plan_for_desc(d, sms, &bn, &pairs, &mt);
+  const long long rows = (pairs || mt == 2) ? 2 * kBlockM : kBlockM;
+  const long long kelems = d.in_dtype == AMOSB_S8 ? 128 : d.in_dtype == AMOSB_F32 ? 32 : 64;
+  long long tiles, kb;
+  if (d.kind == AMOSB_OP_CONV2D_NCHW && conv_is_pointwise_gemm(d)) {
+    const long long pq = d.conv_p * d.conv_q;
+    tiles = d.conv_n * ((d.conv_k + rows - 1) / rows) * ((pq + bn - 1) / bn);
+    kb = (d.conv_c + kelems - 1) / kelems;
+  } else if (conv) {
+    long long nimg = d.conv_n;
+    if (d.kind == AMOSB_OP_CONV2D_HWNC && nimg > 1) nimg = (nimg + kBlockM - 1) / kBlockM * kBlockM;
+    const long long m = nimg * d.conv_p * d.conv_q;
+    tiles = ((m + rows - 1) / rows) * ((d.conv_k + bn - 1) / bn);
+    kb = d.conv_r * d.conv_s * ((d.conv_c + kelems - 1) / kelems);
+  } else {
+    tiles = d.batch * ((d.m + rows - 1) / rows) * ((d.n + bn - 1) / bn);
+    kb = (d.k + kelems - 1) / kelems;
+  }
+  if (kb > 0x7fffffffLL) return 0;
+  return tail_scratch_bytes(tiles, (int)kb, pairs, mt, bn);
 }
 
 int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const void* addend, void* out,
@@ -1045,8 +1277,11 @@ int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const voi
     rc = trailing_ops_for(d, addend, true, &gops);
     if (rc != AMOSB_OK) return rc;
     return run_gemm_core(st, d.in_dtype, d.out_dtype, false, false, true, Nimg, Kout, P * Q, C, d.tile_n,
-                         d.cta_pair, gops, flt, act, out, stream);
+                         d.cta_pair, gops, flt, act, out, workspace, workspace_bytes, device, stream);
   }
+  if (conv_is_pointwise_inplace(d))
+    return run_conv2d_pointwise_inplace(st, d, act, flt, addend, out, workspace, workspace_bytes,
+                                        device, stream);
   long long act_bytes, flt_bytes;
   int c_pad8, c_pad64;
   conv_workspace_layout(d, &act_bytes, &flt_bytes, &c_pad8, &c_pad64);
@@ -1177,14 +1412,16 @@ int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const voi
     p.addend_f16 = cops.f16;
     p.addend = cops.addend;
   }
-  const int grid = p.num_tiles < st->sm_count ? p.num_tiles : st->sm_count;
+  // scratch left behind the two re-laid-out operands: partial sums of a shared-out tail
+  void* sk_ws = static_cast<uint8_t*>(workspace) + act_bytes + flt_bytes;
+  const long long sk_ws_bytes = workspace_bytes - act_bytes - flt_bytes;
   CUtensorMap tmC;
   memset(&tmC, 0, sizeof(tmC));
   if (pairs) {
     p.tiles_m = (int)((Mtot + 2 * kBlockM - 1) / (2 * kBlockM));
     p.num_tiles = (int)conv_tiles_pair;
-    const int npairs =
-        (int)(conv_tiles_pair < st->sm_count / 2 ? conv_tiles_pair : st->sm_count / 2);
+    const int npairs = setup_schedule(&p, st, device, st->sm_count / 2, 2,
+                                      static_cast<size_t>(kBlockM) * bn, sk_ws, sk_ws_bytes);
     if (d.out_dtype == AMOSB_F32)
       return dispatch_pair_bn<0, false, kModeConv, float, false>(bn, tmA, tmB, tmC, p, npairs, stream);
     if (d.out_dtype == AMOSB_F16)
@@ -1192,6 +1429,8 @@ int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const voi
     set_error("conv2d writes float32 or float16");
     return AMOSB_ERR_UNSUPPORTED;
   }
+  const int grid = setup_schedule(&p, st, device, st->sm_count, 1,
+                                  static_cast<size_t>(mt) * kBlockM * bn, sk_ws, sk_ws_bytes);
   if (is_i8) return dispatch_bn<1, false, kModeConv, int32_t, false>(bn, tmA, tmB, tmC, p, grid, stream);
   if (is_tf32) return dispatch_bn<2, false, kModeConv, float, false>(bn, tmA, tmB, tmC, p, grid, stream);
   if (d.out_dtype == AMOSB_F32)
@@ -1207,13 +1446,14 @@ int run_conv2d(const AmosbOpDesc& d, const void* act, const void* flt, const voi
 // filter viewed as a row-major [R*S*C][K] matrix (an MN-major operand), output [N*P*Q][K] row-major.
 // --------------------------------------------------------------------------------------------
 int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, const void* addend,
-                    void* out, int device, cudaStream_t stream) {
+                    void* out, void* workspace, long long workspace_bytes, int device,
+                    cudaStream_t stream) {
   // One image in HWNC is the same memory as one image in NHWC, for the activation and the output
   // alike (the reference's benchmark script runs its layers at batch 1 by default).
   if (d.kind == AMOSB_OP_CONV2D_HWNC && d.conv_n == 1) {
     AmosbOpDesc one = d;
     one.kind = AMOSB_OP_CONV2D_NHWC;
-    return run_conv2d_nhwc(one, act, flt, addend, out, device, stream);
+    return run_conv2d_nhwc(one, act, flt, addend, out, workspace, workspace_bytes, device, stream);
   }
   DeviceState* st = nullptr;
   int rc = get_device_state(device, &st);
@@ -1352,7 +1592,9 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   }
   const bool f32 = d.out_dtype == AMOSB_F32;
   if (is_i8) {
-    const int grid8 = p.num_tiles < st->sm_count ? p.num_tiles : st->sm_count;
+    const int grid8 = setup_schedule(&p, st, device, st->sm_count, 1,
+                                     static_cast<size_t>(mt) * kBlockM * bn, workspace,
+                                     workspace_bytes);
     if (hwnc) {
       if (epi_tma) return dispatch_bn<1, true, kModeConvHwnc, int32_t, true>(bn, tmA, tmB, tmC, p, grid8, stream);
       return dispatch_bn<1, true, kModeConvHwnc, int32_t, false>(bn, tmA, tmB, tmC, p, grid8, stream);
@@ -1364,7 +1606,8 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     const long long tiles_pair = ((Mtot + 2 * kBlockM - 1) / (2 * kBlockM)) * ((Kout + bn - 1) / bn);
     p.tiles_m = (int)((Mtot + 2 * kBlockM - 1) / (2 * kBlockM));
     p.num_tiles = (int)tiles_pair;
-    const int npairs = (int)(tiles_pair < st->sm_count / 2 ? tiles_pair : st->sm_count / 2);
+    const int npairs = setup_schedule(&p, st, device, st->sm_count / 2, 2,
+                                      static_cast<size_t>(kBlockM) * bn, workspace, workspace_bytes);
     if (epi_tma) {
       if (f32) return dispatch_pair_bn<0, true, kModeConvNhwc, float, true>(bn, tmA, tmB, tmC, p, npairs, stream);
       return dispatch_pair_bn<0, true, kModeConvNhwc, __half, true>(bn, tmA, tmB, tmC, p, npairs, stream);
@@ -1372,7 +1615,8 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     if (f32) return dispatch_pair_bn<0, true, kModeConvNhwc, float, false>(bn, tmA, tmB, tmC, p, npairs, stream);
     return dispatch_pair_bn<0, true, kModeConvNhwc, __half, false>(bn, tmA, tmB, tmC, p, npairs, stream);
   }
-  const int grid = p.num_tiles < st->sm_count ? p.num_tiles : st->sm_count;
+  const int grid = setup_schedule(&p, st, device, st->sm_count, 1,
+                                  static_cast<size_t>(mt) * kBlockM * bn, workspace, workspace_bytes);
   if (is_tf32) {
     if (hwnc) {
       if (epi_tma) return dispatch_bn<2, true, kModeConvHwnc, float, true>(bn, tmA, tmB, tmC, p, grid, stream);
@@ -1408,6 +1652,8 @@ int status_peek(int device, int clear) {
   if (clear && v != 0) {
     int zero = 0;
     AMOSB_CUDA_CHECK(cudaMemcpy(st->status_ptr, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    // a kernel that gave up may have left flags of the shared-out tail set
+    AMOSB_CUDA_CHECK(cudaMemset(st->sk_flags, 0, sizeof(unsigned int) * kSkSlots * kSkCtasMax * 4));
   }
   return v;
 }

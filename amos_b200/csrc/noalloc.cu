@@ -74,7 +74,9 @@ extern "C" int amosb_conv2d_nchw_static(const AmosbOpDesc* desc, const AmosbTens
     set_error("expected 2 or 3 inputs and 1 output, got %d inputs and %d outputs", n_in, n_out);
     return AMOSB_ERR_ARG;
   }
-  const int64_t need = amosb_workspace_bytes(desc);
+  // what the call cannot do without (the re-laid-out operands); if the array has room left for the
+  // optional part of the scratch, amosb_run uses it
+  const int64_t need = amosb_workspace_bytes_min(desc);
   if (need < 0) return static_cast<int>(need);
   if (need > kStaticScratchBytes) {
     set_error("this conv2d needs %lld bytes of scratch but the built-in scratch holds %lld "

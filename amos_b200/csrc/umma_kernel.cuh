@@ -22,6 +22,9 @@ constexpr int kBlockM = 128;
 constexpr int kStageKBytes = 128;           // bytes of K per stage row (one 128B swizzle span)
 constexpr int kATileBytes = kBlockM * 128;  // 16 KB
 constexpr int kNumThreads = 256;  // 8 warps: 0 producer, 1 MMA, 2-5 epilogue, 6-7 extra producers
+constexpr int kPwCopyWarps = 4;   // kModeConvPw: warps 8..11 copy the activation
+constexpr int kNumThreadsPw = kNumThreads + 32 * kPwCopyWarps;
+constexpr int umma_threads(int mode) { return mode == 4 ? kNumThreadsPw : kNumThreads; }
 
 // kModeConv: NCHW activation re-laid-out to NHWC scratch + prepacked K-major filter, NCHW output.
 // kModeConvNhwc: NHWC activation and RSCK filter consumed in place (im2col A, MN-major B), NHWC
@@ -32,7 +35,13 @@ constexpr int kNumThreads = 256;  // 8 warps: 0 producer, 1 MMA, 2-5 epilogue, 6
 // times 128 consecutive images: its A operand for a filter tap is a plain tiled box
 // {64 channels, 128 images} of the input pixel (p*st + r*dil - pad, q*st + s*dil - pad), and a
 // pixel outside the image is an out-of-range coordinate that the load fills with zeros.
-enum : int { kModeGemm = 0, kModeConv = 1, kModeConvNhwc = 2, kModeConvHwnc = 3 };
+// kModeConvPw: 1x1, stride-1, unpadded NCHW convolution consumed in place when the channel planes
+// are not 16-byte multiples (so that no tensor map can describe them): GEMM rows are the pixels
+// (n, p, q) flattened, the activation [C][P*Q] of an image is an MN-major A operand that four extra
+// warps copy into the stages with 8-byte cp.async (four pixels each, written straight into the
+// 128-byte-swizzled layout the copy engine would have produced), the KCRS filter is the K-major B
+// operand through TMA, the output is NCHW as in kModeConv.  No re-layout pass, no scratch.
+enum : int { kModeGemm = 0, kModeConv = 1, kModeConvNhwc = 2, kModeConvHwnc = 3, kModeConvPw = 4 };
 enum : int { kEpiAddVec = 1, kEpiAddFull = 2, kEpiRelu = 4, kEpiAddRowVec = 8 };
 
 struct UmmaParams {
@@ -71,6 +80,19 @@ struct UmmaParams {
   int conv_N_real;  // HWNC mode: images that exist (rows past them are computed on zeros, not stored)
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int producers;   // 1..3 threads (in warps 0, 6, 7) issuing the TMA loads, k-blocks dealt round-robin
+  const void* act;  // kModeConvPw: the NCHW activation (16-bit elements)
+  // Shared-out tail.  Whole tiles are dealt round-robin to the CTAs (CTA pairs); when the tile
+  // count does not fill the last round, the k-blocks of the last `sk_tiles` tiles, taken as one
+  // sequence, are cut into equal shares instead, one per worker: worker w gets
+  // sk_q + (w < sk_r) k-blocks starting at w * sk_q + min(w, sk_r).  A share that starts inside a
+  // tile yields partial sums, which its CTA leaves in `sk_partials` (one accumulator tile per
+  // CTA, 32-bit) and announces in `sk_flags` ([CTA][4], one per epilogue warp); the CTA whose
+  // share holds the tile's first k-block adds them to its own and stores the tile.
+  int sk_tiles;   // 0: every tile is computed whole by one worker
+  int sk_first;   // first shared tile (= num_tiles - sk_tiles)
+  int sk_q, sk_r;
+  uint32_t* sk_partials;
+  unsigned int* sk_flags;
   // Nanoseconds after which a wait on an mbarrier is given up (the CTA then raises its abort flag,
   // records a status code and leaves).  An epilogue wait spans the whole k-loop of a tile, each of
   // whose own waits has this budget, so it gets twice as much.
@@ -79,6 +101,126 @@ struct UmmaParams {
   // thread's first wait runs out with nothing in flight.  The way the give-up path is exercised.
   int diag_no_loads;
 };
+
+// One piece of a worker's schedule: k-blocks [kb_begin, kb_end) of `tile`.
+struct Segment {
+  int tile, kb_begin, kb_end;
+};
+// The schedule of worker `w` of `nw`: first its share of the shared-out tail (so that partial
+// sums are ready long before the CTA that adds them up asks), then its whole tiles.  Every role
+// of a CTA walks the same sequence.
+struct SegmentIter {
+  long long u, u_end;  // next and end unit (k-block of the shared tiles' sequence) of the share
+  int dp_tile, nw;
+  __device__ __forceinline__ SegmentIter(const UmmaParams& p, int w, int workers) {
+    nw = workers;
+    dp_tile = w;
+    if (p.sk_tiles > 0) {
+      u = static_cast<long long>(w) * p.sk_q + min(w, p.sk_r);
+      u_end = u + p.sk_q + (w < p.sk_r ? 1 : 0);
+    } else {
+      u = u_end = 0;
+    }
+  }
+  __device__ __forceinline__ bool next(const UmmaParams& p, Segment& s) {
+    if (u < u_end) {
+      const int t = static_cast<int>(u / p.num_kb);
+      const int kb = static_cast<int>(u - static_cast<long long>(t) * p.num_kb);
+      const int len = static_cast<int>(min(static_cast<long long>(p.num_kb - kb), u_end - u));
+      s.tile = p.sk_first + t;
+      s.kb_begin = kb;
+      s.kb_end = kb + len;
+      u += len;
+      return true;
+    }
+    if (dp_tile < p.sk_first) {
+      s.tile = dp_tile;
+      s.kb_begin = 0;
+      s.kb_end = p.num_kb;
+      dp_tile += nw;
+      return true;
+    }
+    return false;
+  }
+};
+// Worker whose share holds unit `u` of the shared tiles' sequence.
+__device__ __forceinline__ int sk_worker_of(const UmmaParams& p, long long u) {
+  const long long big = static_cast<long long>(p.sk_r) * (p.sk_q + 1);
+  if (u < big) return static_cast<int>(u / (p.sk_q + 1));
+  return p.sk_r + static_cast<int>((u - big) / p.sk_q);
+}
+constexpr int kStatusTimeoutPartials = 106;  // an epilogue warp waited for another CTA's partial sums
+
+// Bounded wait for a flag in global memory that another CTA of this grid sets (all CTAs of the
+// grid are resident: the grid never exceeds one CTA per SM).
+__device__ __forceinline__ bool gflag_wait(const unsigned int* flag, volatile int* abort_flag,
+                                           int* status, uint64_t budget_ns) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v != 0) return true;
+    if ((++spins & 0x3Fu) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > budget_ns) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, kStatusTimeoutPartials);
+        return false;
+      }
+    }
+  }
+}
+
+// The two halves of the exchange of partial sums, kept out of line: they run for a handful of
+// tiles per launch, and inlined into the epilogue's chunk loop they cost every kernel 70 registers
+// and a third of its speed on short shapes.  `taddr_row` = this warp's lane quarter, first column
+// of the accumulator; COLS = accumulator columns of the CTA's tile (MT * BN).  A partial tile is
+// laid out [column][128 rows], so a warp moves 128 contiguous bytes per register.
+//
+// Contributor: the raw accumulator words go to this CTA's slot (`dst` = slot + this thread's row).
+template <int COLS>
+__device__ __noinline__ void sk_dump_partials(uint32_t taddr_row, uint32_t* dst) {
+  uint32_t r[32];
+#pragma unroll 1
+  for (int c = 0; c < COLS / 32; ++c) {
+    tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>(c * 32), r);
+    tmem_ld_wait_regs(r);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) __stcg(dst + (static_cast<size_t>(c) * 32 + j) * kBlockM, r[j]);
+  }
+}
+// Finisher: the partial sums that workers first..last left in their slots (`src` = slot 0 + this
+// thread's row; slots `slot_stride` words apart) are added into the accumulator in TMEM, in worker
+// order; the ordinary epilogue then runs on the completed sums.
+template <int KIND, int COLS>
+__device__ __noinline__ void sk_add_partials(uint32_t taddr_row, const uint32_t* src, int first,
+                                             int last, size_t slot_stride) {
+  uint32_t r[32];
+#pragma unroll 1
+  for (int c = 0; c < COLS / 32; ++c) {
+    tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>(c * 32), r);
+    tmem_ld_wait_regs(r);
+    for (int cw = first; cw <= last; ++cw) {
+      const uint32_t* s = src + static_cast<size_t>(cw) * slot_stride +
+                          (static_cast<size_t>(c) * 32) * kBlockM;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t v = __ldcg(s + j * kBlockM);
+        if constexpr (KIND == 1) {
+          r[j] += v;  // int32 sums: exact in any order
+        } else {
+          r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(v));
+        }
+      }
+    }
+    tmem_st_32x32b_x32(taddr_row + static_cast<uint32_t>(c * 32), r);
+  }
+  tmem_st_wait();
+}
 
 // Output staging of the TMA-store epilogue: per epilogue warp kEpiBufs buffers of 32 rows x 128
 // bytes, used in rotation; a buffer is rewritten once the store issued kEpiBufs stores ago has
@@ -117,6 +259,18 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
                "r"(d)
                : "memory");
+}
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+// 8-byte read of data that is used once: no L1 allocation (the L1 beside ~200 KB of stages is
+// small, and lines allocated for in-flight loads would cap how many can be outstanding).
+__device__ __forceinline__ uint2 ldg_stream_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];"
+               : "=r"(v.x), "=r"(v.y)
+               : "l"(p));
+  return v;
 }
 __device__ __forceinline__ uint32_t pack_half2(uint32_t lo_f32_bits, uint32_t hi_f32_bits) {
   __half2 h = __floats2half2_rn(__uint_as_float(lo_f32_bits), __uint_as_float(hi_f32_bits));
@@ -237,13 +391,15 @@ __device__ __forceinline__ void store_row_chunk(OutT* __restrict__ dst, const ui
 // MN-major operand, in chunks of 128 bytes of M like an MN-major B.  GEMM mode, MT = 1 only.
 template <int KIND, int BN, bool B_MN_MAJOR, int MODE, typename OutT, bool EPI_TMA, int MT = 1,
           bool A_MN_MAJOR = false>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(umma_threads(MODE), 1)
 umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                        const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmC, const UmmaParams p) {
   using Cfg = UmmaConfig<BN, EPI_TMA, MT>;
   constexpr int kTileRows = kBlockM * MT;  // output rows of one CTA tile
-  static_assert(!EPI_TMA || MODE != kModeConv, "the TMA-store epilogue writes row-major C");
+  static_assert(!EPI_TMA || (MODE != kModeConv && MODE != kModeConvPw),
+                "the TMA-store epilogue writes row-major C");
+  constexpr bool kNchwOut = MODE == kModeConv || MODE == kModeConvPw;  // output stored as NCHW
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPer128B = (KIND == 0) ? 64 : (KIND == 1) ? 128 : 32;  // K elements per stage; also MN chunk
   constexpr int kUmmaKRows = (KIND == 0) ? 16 : (KIND == 1) ? 32 : 8;       // K per MMA instruction
@@ -254,7 +410,10 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   static_assert(MODE != kModeConv || !B_MN_MAJOR, "NCHW conv consumes a K-major prepacked filter");
   static_assert(MODE != kModeConvNhwc || B_MN_MAJOR, "NHWC conv reads the RSCK filter MN-major");
   static_assert(MODE != kModeConvHwnc || B_MN_MAJOR, "HWNC conv reads the RSCK filter MN-major");
-  static_assert(!A_MN_MAJOR || (MODE == kModeGemm && MT == 1), "MN-major A: plain GEMM tiles only");
+  static_assert(!A_MN_MAJOR || ((MODE == kModeGemm || MODE == kModeConvPw) && MT == 1),
+                "MN-major A: 128-row tiles of the GEMM and of the in-place 1x1 convolution");
+  static_assert(MODE != kModeConvPw || (A_MN_MAJOR && !B_MN_MAJOR && KIND == 0),
+                "in-place 1x1 NCHW: 16-bit activation as MN-major A, KCRS filter as K-major B");
   constexpr int kAChunks = kBlockM / kElemsPer128B;  // MN-major A: 128-byte chunks of M per stage
 
   extern __shared__ uint8_t smem_raw[];
@@ -282,7 +441,9 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     prefetch_tensormap(&tmB);
     if constexpr (EPI_TMA) prefetch_tensormap(&tmC);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      // one arrival of the TMA-issuing thread (with the bytes it expects), plus one per copying
+      // thread where the activation is brought in by cp.async
+      mbar_init(full_bar(s), MODE == kModeConvPw ? 1 + 32 * kPwCopyWarps : 1);
       mbar_init(empty_bar(s), MT);  // one commit per MMA-issuing thread
     }
     for (int s = 0; s < 2; ++s) {
@@ -326,7 +487,76 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr bool kSecondIssuer = MT == 2;
   const bool is_producer_warp = warp == 0 || warp == 6 || (warp == 7 && !kSecondIssuer);
   const bool is_mma_warp = warp == 1 || (warp == 7 && kSecondIssuer);
-  if (is_producer_warp) {
+  if (MODE == kModeConvPw && warp >= 8) {
+    // ================================================================ activation copier (1x1 NCHW)
+    // A stage's A tile is 64 channels (k-rows) x 128 pixels, stored as the copy engine stores an
+    // MN-major tile: two chunks of 64 pixels, each 64 rows of 128 bytes, the 16-byte units of a
+    // row XOR-ed with the row number (128-byte swizzle).  Lane g of a warp owns the four pixels
+    // 4g..4g+3 of the tile (8 bytes); a warp instruction therefore moves one whole channel row of
+    // the tile, 256 contiguous bytes of global memory.  Warp w of the four moves channels
+    // 16w..16w+15 of every k-block.  P*Q is a multiple of 4, so a pixel quad never straddles two
+    // images and is 8-byte aligned.
+    // One cp.async moves a lane's 8 bytes straight into the stage, and the stage's barrier is told
+    // to count this thread's arrival once the copies it has issued so far have landed
+    // (cp.async.mbarrier.arrive.noinc): nothing in this loop waits for data, so a CTA has all the
+    // stages but the one being multiplied in flight.  (Waiting in line for an earlier group before
+    // issuing the next one kept only two groups in flight and ran at half the rate: the loop's
+    // period was half the memory latency.)
+    if constexpr (MODE == kModeConvPw) {
+      grid_dependency_wait();
+      const int cwp = warp - 8;
+      const uint32_t g = lane;
+      const uint32_t dst_lane = (g >> 4) * kBChunkBytes + (g & 1u) * 8u;
+      const uint32_t unit = (g & 15u) >> 1;
+      const uint8_t* const act = static_cast<const uint8_t*>(p.act);
+      const long long plane_bytes = static_cast<long long>(p.PQ) * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = !p.diag_no_loads;
+      SegmentIter it(p, blockIdx.x, gridDim.x);
+      Segment sg;
+      while (ok && it.next(p, sg)) {
+        int b, m_blk, n_blk;
+        decode_tile(sg.tile, b, m_blk, n_blk);
+        const int m = m_blk * kBlockM + 4 * static_cast<int>(g);
+        const bool row_ok = m < p.M;
+        const int img = row_ok ? m / p.PQ : 0;
+        const int pq = row_ok ? m - img * p.PQ : 0;
+        const uint8_t* src_lane =
+            act + (static_cast<long long>(img) * p.conv_C * p.PQ + pq) * 2;
+        for (int kb = sg.kb_begin; kb < sg.kb_end; ++kb) {
+          bool got = true;
+          if (lane == 0)
+            got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                            kStatusTimeoutProducer, p.wait_budget_ns);
+          got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+          if (!got) {
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + stage * Cfg::kStageBytes;
+          const int c0 = cwp * 16;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int c = c0 + i;                        // k-row inside the stage
+            const int chan = kb * kElemsPer128B + c;     // channel of the layer
+            const bool live = row_ok && chan < p.conv_C;
+            const uint8_t* src = live ? src_lane + chan * plane_bytes : act;
+            const uint32_t dst = sA + dst_lane + static_cast<uint32_t>(c) * 128u +
+                                 ((unit ^ (static_cast<uint32_t>(c) & 7u)) << 4);
+            cp_async_8(dst, src, live ? 8u : 0u);
+          }
+          cp_async_arrive_noinc(full_bar(stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // nothing may be in flight when the CTA's shared memory is given up
+      cp_async_wait_all();
+    }
+  } else if (is_producer_warp) {
     // ================================================================ TMA producer
     // Up to three issuing threads (lane 0 of warps 0, 6, 7).  The CTA's k-blocks form one stream
     // across its tiles; thread pi owns k-blocks pi, pi + P, pi + 2P, ... of that stream and arms
@@ -335,7 +565,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     // and compares: positions (stage, filter tap, channel chunk) advance by P steps at a time.
     const int pi = warp == 0 ? 0 : warp - 5;
     // stage = pi + j * P below needs P <= kStages
-    const int P = min(min(p.producers, kSecondIssuer ? 2 : 3), kStages);
+    const int P = MODE == kModeConvPw ? 1 : min(min(p.producers, kSecondIssuer ? 2 : 3), kStages);
     if (lane == 0 && pi < P && !p.diag_no_loads) {
       // the kernel may have been started while its predecessor in the stream was still running
       // (for the NCHW conv that is the re-layout kernel that writes both operands): nothing is
@@ -349,16 +579,20 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       long long rc_wait = 0;
       const long long rc_begin = clock64();
 #endif
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        if (kb >= p.num_kb) {  // fewer k-blocks in a tile than issuing threads
-          kb -= p.num_kb;
+      SegmentIter it(p, blockIdx.x, gridDim.x);
+      Segment sg;
+      while (ok && it.next(p, sg)) {
+        // `kb` counts inside the segment; the k-block it names is sg.kb_begin + kb
+        const int seg_len = sg.kb_end - sg.kb_begin;
+        if (kb >= seg_len) {  // fewer k-blocks in the segment than issuing threads
+          kb -= seg_len;
           continue;
         }
         int b, m_blk, n_blk;
-        decode_tile(tile, b, m_blk, n_blk);
+        decode_tile(sg.tile, b, m_blk, n_blk);
         int cw[MT], ch[MT], cn[MT];  // im2col start of each 128-row sub-tile
         int cc = 0, fs = 0, fr = 0;  // channel chunk and filter tap of k-block kb
-        if constexpr (MODE != kModeGemm) {
+        if constexpr (MODE != kModeGemm && MODE != kModeConvPw) {
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const int m0 = m_blk * kTileRows + mt * kBlockM;
@@ -375,12 +609,13 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             cw[mt] = oq * p.stride_w - p.pad_w;
             ch[mt] = op * p.stride_h - p.pad_h;
           }
-          const int rs = kb / p.c_chunks;
-          cc = kb - rs * p.c_chunks;
+          const int rs = (sg.kb_begin + kb) / p.c_chunks;
+          cc = (sg.kb_begin + kb) - rs * p.c_chunks;
           fr = rs / p.S;
           fs = rs - fr * p.S;
         }
-        for (; kb < p.num_kb; kb += P) {
+        for (; kb < seg_len; kb += P) {
+          const int kabs = sg.kb_begin + kb;
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t0 = clock64();
 #endif
@@ -402,11 +637,14 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #define AMOSB_DBG_A if (!dbg_no_a)
 #define AMOSB_DBG_B if (!dbg_no_b)
 #else
-          mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+          mbar_arrive_expect_tx(fb, MODE == kModeConvPw ? Cfg::kBTileBytes : Cfg::kStageBytes);
 #define AMOSB_DBG_A
 #define AMOSB_DBG_B
 #endif
-          if constexpr (MODE == kModeGemm) {
+          if constexpr (MODE == kModeConvPw) {
+            // the filter [K_out][C] is the K-major B operand; channels past C load as zeros
+            AMOSB_DBG_B tma_load_2d(sB, &tmB, fb, kabs * kElemsPer128B, n_blk * BN);
+          } else if constexpr (MODE == kModeGemm) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               // rows past M are zero-filled by the load and still counted in the stage's bytes
@@ -414,11 +652,11 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
                 for (int j = 0; j < kAChunks; ++j) {
                   AMOSB_DBG_A tma_load_3d(sA + j * kBChunkBytes, &tmA, fb,
-                                          m_blk * kBlockM + j * kElemsPer128B, kb * kElemsPer128B,
+                                          m_blk * kBlockM + j * kElemsPer128B, kabs * kElemsPer128B,
                                           p.a_bcast ? 0 : b);
                 }
               } else {
-                AMOSB_DBG_A tma_load_3d(sA + mt * kATileBytes, &tmA, fb, kb * kElemsPer128B,
+                AMOSB_DBG_A tma_load_3d(sA + mt * kATileBytes, &tmA, fb, kabs * kElemsPer128B,
                                         m_blk * kTileRows + mt * kBlockM, p.a_bcast ? 0 : b);
               }
             }
@@ -426,10 +664,10 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
               for (int j = 0; j < kBChunks; ++j) {
                 AMOSB_DBG_B tma_load_3d(sB + j * kBChunkBytes, &tmB, fb, n_blk * BN + j * kElemsPer128B,
-                            kb * kElemsPer128B, b);
+                            kabs * kElemsPer128B, b);
               }
             } else {
-              AMOSB_DBG_B tma_load_3d(sB, &tmB, fb, kb * kElemsPer128B, n_blk * BN, b);
+              AMOSB_DBG_B tma_load_3d(sB, &tmB, fb, kabs * kElemsPer128B, n_blk * BN, b);
             }
           } else {
 #pragma unroll
@@ -447,7 +685,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
               }
             }
             if constexpr (MODE == kModeConv) {
-              AMOSB_DBG_B tma_load_2d(sB, &tmB, fb, kb * kElemsPer128B, n_blk * BN);
+              AMOSB_DBG_B tma_load_2d(sB, &tmB, fb, kabs * kElemsPer128B, n_blk * BN);
             } else {
               // RSCK filter as [R*S*C][K]: rows of tap rs start at rs*C; channels past C multiply
               // activation columns that the im2col load zero-fills
@@ -475,7 +713,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             phase ^= 1u;
           }
         }
-        kb -= p.num_kb;
+        kb -= seg_len;
       }
 #ifdef AMOSB_ROLE_CYCLES
       if (pi == 0) {
@@ -500,7 +738,9 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       long long rc_full = 0, rc_tmem = 0;
       const long long rc_begin = clock64();
 #endif
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      SegmentIter it(p, blockIdx.x, gridDim.x);
+      Segment sg;
+      while (ok && it.next(p, sg)) {
 #ifdef AMOSB_ROLE_CYCLES
         const long long rc_t1 = clock64();
 #endif
@@ -514,7 +754,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #endif
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * Cfg::kAccCols);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = sg.kb_begin; kb < sg.kb_end; ++kb) {
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t0 = clock64();
 #endif
@@ -525,6 +765,9 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #ifdef AMOSB_ROLE_CYCLES
           rc_full += clock64() - rc_t0;
 #endif
+          // cp.async wrote the activation through the generic proxy; the MMA reads it through
+          // the asynchronous one
+          if constexpr (MODE == kModeConvPw) fence_proxy_async_smem();
           tc_fence_after_sync();
           const uint32_t sA = smem_base + stage * Cfg::kStageBytes;
           const uint32_t sB = sA + MT * kATileBytes;
@@ -542,7 +785,8 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                 tmem_d + static_cast<uint32_t>(mt * BN),
                 smem_desc_lo(sA + mt * kATileBytes, A_MN_MAJOR ? kBChunkBytes : 16), b_lo,
                 A_MN_MAJOR ? kHiMn : smem_desc_hi_sw128(1024),
-                B_MN_MAJOR ? kHiMn : smem_desc_hi_sw128(1024), idesc, kb != 0 ? 1u : 0u);
+                B_MN_MAJOR ? kHiMn : smem_desc_hi_sw128(1024), idesc,
+                kb != sg.kb_begin ? 1u : 0u);  // the segment's first MMA overwrites
           }
           umma_commit(empty_bar(stage));  // smem slot reusable once these MMAs have read it
           if (++stage == kStages) {
@@ -585,9 +829,13 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     long long rc_wait = 0;
     const long long rc_begin = clock64();
 #endif
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    constexpr size_t kPartialElems = static_cast<size_t>(MT) * kBlockM * BN;  // per CTA slot
+    const int worker = blockIdx.x;
+    SegmentIter it(p, worker, gridDim.x);
+    Segment sg;
+    while (ok && it.next(p, sg)) {
       int b, m_blk, n_blk;
-      decode_tile(tile, b, m_blk, n_blk);
+      decode_tile(sg.tile, b, m_blk, n_blk);
 #ifdef AMOSB_ROLE_CYCLES
       const long long rc_t0 = clock64();
 #endif
@@ -599,6 +847,57 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       rc_wait += clock64() - rc_t0;
 #endif
       tc_fence_after_sync();
+      // Part of a shared-out tile?  A segment that does not start at the tile's first k-block
+      // leaves its sums for the CTA that holds the first k-block; that CTA, if its segment stops
+      // short of the last k-block, adds the sums of the workers after it (their shares follow
+      // its own without a gap) before the usual epilogue.
+      const bool sk_contrib = sg.kb_begin > 0;
+      int fix_first = 0, fix_last = -1;
+      if (!sk_contrib && sg.kb_end < p.num_kb) {
+        fix_first = worker + 1;
+        fix_last = sk_worker_of(
+            p, static_cast<long long>(sg.tile - p.sk_first) * p.num_kb + p.num_kb - 1);
+        bool got = true;
+        if (lane == 0) {
+          for (int cw = fix_first; got && cw <= fix_last; ++cw)
+            got = gflag_wait(p.sk_flags + cw * 4 + quarter, abort_flag, p.status,
+                             2 * p.wait_budget_ns);
+        }
+        if (__shfl_sync(0xffffffffu, got ? 1 : 0, 0) == 0) {
+          ok = false;
+          break;
+        }
+      }
+      if (sk_contrib || fix_last >= fix_first) {
+        const uint32_t taddr_q = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                 static_cast<uint32_t>(acc * Cfg::kAccCols);
+        const size_t part_lane = static_cast<size_t>(quarter * 32) + lane;
+        if (sk_contrib) {
+          sk_dump_partials<Cfg::kAccCols>(
+              taddr_q, p.sk_partials + static_cast<size_t>(worker) * kPartialElems + part_lane);
+          __threadfence();  // the partial sums are in L2 before the flag says so
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + worker * 4 + quarter),
+                         "r"(1u)
+                         : "memory");
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+          continue;
+        }
+        sk_add_partials<KIND, Cfg::kAccCols>(taddr_q, p.sk_partials + part_lane, fix_first, fix_last,
+                                             kPartialElems);
+        __syncwarp();  // every lane has read its partial sums: the flags can be reused
+        if (lane == 0) {
+          for (int cw = fix_first; cw <= fix_last; ++cw) p.sk_flags[cw * 4 + quarter] = 0u;
+        }
+      }
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {  // the 128-row accumulator tiles of this CTA tile
       const int row = m_blk * kTileRows + mt * kBlockM + quarter * 32 + static_cast<int>(lane);
@@ -702,7 +1001,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         });
       } else {
         OutT* row_ptr = nullptr;
-        if constexpr (MODE != kModeConv) {
+        if constexpr (!kNchwOut) {
           row_ptr = out + static_cast<long long>(b) * p.c_batch_stride +
                     static_cast<long long>(orow) * p.ldc;
         } else {
@@ -715,7 +1014,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           const int ncols_valid = p.N - col0;
           if (p.epi_flags != 0) {
             long long off, stride;
-            if constexpr (MODE != kModeConv) {
+            if constexpr (!kNchwOut) {
               off = (p.epi_flags & kEpiAddRowVec)
                         ? static_cast<long long>(row)
                         : static_cast<long long>(b) * p.c_batch_stride +
@@ -732,7 +1031,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row_ok, fp, stride);
           }
           if (row_ok) {
-            if constexpr (MODE != kModeConv) {
+            if constexpr (!kNchwOut) {
               store_row_chunk<OutT>(row_ptr + col0, r, ncols_valid);
             } else {
               // NCHW: lanes of a warp are consecutive pixels of one channel plane -> coalesced.

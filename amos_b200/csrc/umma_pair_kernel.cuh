@@ -111,9 +111,9 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     n_blk = r / gm;
   };
 
-  // A pair's work units are whole 256 x BN tiles.  (Cutting the tiles of a partial last wave into
-  // column slices, or into halves of the reduction, was tried: a pair MMA of half the width
-  // costs its issuing thread the same, and the large GEMMs are bound by power, so neither paid.)
+  // A pair's work units are whole 256 x BN tiles, or k-block ranges of them where the schedule
+  // shares out a short last round (see SegmentIter).  (Cutting tiles into column slices was tried:
+  // a pair MMA of half the width costs its issuing thread the same, so it did not pay.)
   constexpr int n_off = 0;
   constexpr int width = BN;
 
@@ -137,14 +137,17 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       long long rc_wait = 0;
       const long long rc_begin = clock64();
 #endif
-      for (int unit = pair_id; ok && unit < p.num_tiles; unit += num_pairs) {
-        if (kb >= p.num_kb) {  // fewer k-blocks in a unit than issuing threads
-          kb -= p.num_kb;
+      SegmentIter it(p, pair_id, num_pairs);
+      Segment sg;
+      while (ok && it.next(p, sg)) {
+        // `kb` counts inside the segment; the k-block it names is sg.kb_begin + kb
+        const int seg_len = sg.kb_end - sg.kb_begin;
+        if (kb >= seg_len) {  // fewer k-blocks in the segment than issuing threads
+          kb -= seg_len;
           continue;
         }
-        const int tile = unit;
         int b, m_blk, n_blk;
-        decode_tile(tile, b, m_blk, n_blk);
+        decode_tile(sg.tile, b, m_blk, n_blk);
         const int m0 = m_blk * kPairM + static_cast<int>(rank) * kBlockM;  // first row of this CTA
         const int half = width >> 1;                                       // B columns of this CTA
         const int n_half0 = n_blk * BN + n_off + static_cast<int>(rank) * half;
@@ -158,12 +161,13 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int oq = pq - op * p.Q;
           cw = oq * p.stride_w - p.pad_w;
           ch = op * p.stride_h - p.pad_h;
-          const int rs = kb / p.c_chunks;
-          cc = kb - rs * p.c_chunks;
+          const int rs = (sg.kb_begin + kb) / p.c_chunks;
+          cc = (sg.kb_begin + kb) - rs * p.c_chunks;
           fr = rs / p.S;
           fs = rs - fr * p.S;
         }
-        for (; kb < p.num_kb; kb += P) {
+        for (; kb < seg_len; kb += P) {
+          const int kabs = sg.kb_begin + kb;
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t0 = clock64();
 #endif
@@ -180,16 +184,16 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t fb = full_bar(stage);  // credited on the leader's copy of this barrier
           if (rank == 0) mbar_arrive_expect_tx(fb, stage_tx);
           if constexpr (MODE == kModeGemm) {
-            tma_load_3d_pair(sA, &tmA, fb, kb * kElemsPer128B, m0, p.a_bcast ? 0 : b);
+            tma_load_3d_pair(sA, &tmA, fb, kabs * kElemsPer128B, m0, p.a_bcast ? 0 : b);
             if constexpr (B_MN_MAJOR) {
               for (int j = 0; j * kElemsPer128B < half; ++j) {
                 tma_load_3d_pair(sB + j * kBChunkBytes, &tmB, fb, n_half0 + j * kElemsPer128B,
-                                 kb * kElemsPer128B, b);
+                                 kabs * kElemsPer128B, b);
               }
             } else {
               // K-major B arrives in boxes of 64 rows
               for (int j = 0; j * 64 < half; ++j) {
-                tma_load_3d_pair(sB + j * 64 * 128, &tmB, fb, kb * kElemsPer128B, n_half0 + j * 64, b);
+                tma_load_3d_pair(sB + j * 64 * 128, &tmB, fb, kabs * kElemsPer128B, n_half0 + j * 64, b);
               }
             }
           } else {
@@ -198,7 +202,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                     static_cast<uint16_t>(fr * p.dil_h));
             if constexpr (MODE == kModeConv) {
               for (int j = 0; j * 64 < half; ++j) {
-                tma_load_2d_pair(sB + j * 64 * 128, &tmB, fb, kb * 64, n_half0 + j * 64);
+                tma_load_2d_pair(sB + j * 64 * 128, &tmB, fb, kabs * 64, n_half0 + j * 64);
               }
             } else {
               const int brow = (fr * p.S + fs) * p.conv_C + cc * 64;
@@ -222,7 +226,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             phase ^= 1u;
           }
         }
-        kb -= p.num_kb;
+        kb -= seg_len;
       }
 #ifdef AMOSB_ROLE_CYCLES
       if (pi == 0) {
@@ -243,8 +247,9 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       long long rc_full = 0, rc_tmem = 0, rc_issue = 0, rc_commit = 0;
       const long long rc_begin = clock64();
 #endif
-      for (int unit = pair_id; ok && unit < p.num_tiles; unit += num_pairs) {
-        const int tile = unit;
+      SegmentIter it(p, pair_id, num_pairs);
+      Segment sg;
+      while (ok && it.next(p, sg)) {
         const uint32_t idesc = make_idesc<KIND>(kPairM, width, B_MN_MAJOR) | p.idesc_formats;
 #ifdef AMOSB_ROLE_CYCLES
         const long long rc_t1 = clock64();
@@ -259,7 +264,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #endif
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = sg.kb_begin; kb < sg.kb_end; ++kb) {
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t0 = clock64();
 #endif
@@ -282,7 +287,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                                    smem_desc_lo(sB, B_MN_MAJOR ? kBChunkBytes : 16),
                                                    smem_desc_hi_sw128(1024),
                                                    smem_desc_hi_sw128(1024), idesc,
-                                                   kb != 0 ? 1u : 0u);
+                                                   kb != sg.kb_begin ? 1u : 0u);
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t3 = clock64();
           rc_issue += rc_t3 - rc_t2;
@@ -331,10 +336,13 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     long long rc_wait = 0;
     const long long rc_begin = clock64();
 #endif
-    for (int unit = pair_id; ok && unit < p.num_tiles; unit += num_pairs) {
-      const int tile = unit;
+    constexpr size_t kPartialElems = static_cast<size_t>(kBlockM) * BN;  // per CTA slot
+    const int my_slot = blockIdx.x;  // a pair's two CTAs keep the sums of their own 128 rows
+    SegmentIter it(p, pair_id, num_pairs);
+    Segment sg;
+    while (ok && it.next(p, sg)) {
       int b, m_blk, n_blk;
-      decode_tile(tile, b, m_blk, n_blk);
+      decode_tile(sg.tile, b, m_blk, n_blk);
 #ifdef AMOSB_ROLE_CYCLES
       const long long rc_t0 = clock64();
 #endif
@@ -346,6 +354,58 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       rc_wait += clock64() - rc_t0;
 #endif
       tc_fence_after_sync();
+      // shared-out tile: see the single-CTA kernel; the workers are pairs, and the CTA of rank r
+      // exchanges sums with the CTAs of rank r of the other pairs
+      const bool sk_contrib = sg.kb_begin > 0;
+      int fix_first = 0, fix_last = -1;
+      if (!sk_contrib && sg.kb_end < p.num_kb) {
+        fix_first = pair_id + 1;
+        fix_last = sk_worker_of(
+            p, static_cast<long long>(sg.tile - p.sk_first) * p.num_kb + p.num_kb - 1);
+        bool got = true;
+        if (lane == 0) {
+          for (int cw = fix_first; got && cw <= fix_last; ++cw)
+            got = gflag_wait(p.sk_flags + (2 * cw + static_cast<int>(rank)) * 4 + quarter,
+                             abort_flag, p.status, 2 * p.wait_budget_ns);
+        }
+        if (__shfl_sync(0xffffffffu, got ? 1 : 0, 0) == 0) {
+          ok = false;
+          break;
+        }
+      }
+      if (sk_contrib || fix_last >= fix_first) {
+        const uint32_t taddr_q =
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+        const size_t part_lane = static_cast<size_t>(quarter * 32) + lane;
+        if (sk_contrib) {
+          sk_dump_partials<BN>(taddr_q,
+                               p.sk_partials + static_cast<size_t>(my_slot) * kPartialElems + part_lane);
+          __threadfence();  // the partial sums are in L2 before the flag says so
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + my_slot * 4 + quarter),
+                         "r"(1u)
+                         : "memory");
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_leader(tmem_empty_bar(acc));
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+          continue;
+        }
+        // slot of pair cw's CTA of this rank: 2 * cw + rank
+        sk_add_partials<KIND, BN>(taddr_q,
+                                  p.sk_partials + static_cast<size_t>(rank) * kPartialElems + part_lane,
+                                  fix_first, fix_last, 2 * kPartialElems);
+        __syncwarp();  // every lane has read its partial sums: the flags can be reused
+        if (lane == 0) {
+          for (int cw = fix_first; cw <= fix_last; ++cw)
+            p.sk_flags[(2 * cw + static_cast<int>(rank)) * 4 + quarter] = 0u;
+        }
+      }
       const int row0 = m_blk * kPairM + static_cast<int>(rank) * kBlockM + quarter * 32;
       const int row = row0 + static_cast<int>(lane);
       const uint32_t taddr_row =

@@ -451,7 +451,7 @@ def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_st
         res["shard_rel_l2"] = rel
         # integers must match bit for bit; floats may differ by the order of the fp32 additions
         # when the shard picks a tile family that splits the reduction
-        res["shard_ok"] = 1.0 if (exact or (not integer and rel <= 2e-6)) else 0.0
+        res["shard_ok"] = 1.0 if (exact or (not integer and rel <= 1e-5)) else 0.0
         del full_ins, full_out
 
     if time_gather and world > 1 and not weak:

@@ -127,12 +127,23 @@ int amosb_recognize(const char* te_dag, AmosbOpDesc* out);
 
 /*
  * Scratch memory (bytes, device global memory, 1024-byte aligned) that amosb_run needs for `desc`:
- * the NHWC copy of the activation and the re-laid-out filter of the NCHW conv path; 0 for the GEMM
- * family, for NHWC convolutions (consumed in place) and for 1x1 NCHW layers that run as GEMMs.  Counterpart of the workspace the reference's generated host code obtains through
+ * the NHWC copy of the activation and the re-laid-out filter of the NCHW conv path (nothing of the
+ * kind for the GEMM family, for NHWC / HWNC convolutions and for 1x1 NCHW layers, which are consumed
+ * in place), plus an optional part described under amosb_workspace_bytes_min.  Counterpart of the workspace the reference's generated host code obtains through
  * TVMBackendAllocWorkspace (reference: include/tvm/runtime/c_backend_api.h:49-91); here the caller
  * allocates it.  Returns a negative error code on a bad descriptor.
  */
 int64_t amosb_workspace_bytes(const AmosbOpDesc* desc);
+
+/*
+ * The part of amosb_workspace_bytes(desc) that amosb_run cannot do without: the re-laid-out
+ * operands of the NCHW conv path, 0 for everything else.  The rest is optional: room for the partial
+ * sums that CTAs exchange when the tiles of the last, short round of a schedule are shared out
+ * among all SMs (up to ~19 MB; where the tile count fills its last round it is 0).  With less than
+ * the full amount -- or workspace == NULL for operators whose minimum is 0 -- amosb_run computes
+ * the same numbers with every tile on one CTA, somewhat slower.  No counterpart in the reference.
+ */
+int64_t amosb_workspace_bytes_min(const AmosbOpDesc* desc);
 
 /*
  * Run the operator: the counterpart of calling the built module, `func(A, B, C)`
@@ -182,7 +193,7 @@ int amosb_describe_plan(const AmosbOpDesc* desc, int device, char* buf, int buf_
  * (AMOSB_STATIC_SCRATCH_BYTES usable bytes; every GPU that loads the library holds it until the
  * process exits).  The caller passes only inputs and output, exactly as for amosb_run; no
  * cudaMalloc, cudaFree or other allocating routine is called.
- *  - Descriptors whose amosb_workspace_bytes() exceeds AMOSB_STATIC_SCRATCH_BYTES are refused
+ *  - Descriptors whose amosb_workspace_bytes_min() exceeds AMOSB_STATIC_SCRATCH_BYTES are refused
  *    with AMOSB_ERR_UNSUPPORTED and a message naming both sizes.
  *  - The first call on a device resolves the array's device address (and does the library's
  *    one-time device set-up); make that first call before any stream capture begins.

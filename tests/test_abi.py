@@ -40,14 +40,32 @@ def test_version_and_error_string(built_lib):
 
 
 def test_workspace_bytes(built_lib):
-    assert _lib.workspace_bytes(_lib.gemm_desc(128, 128, 128)) == 0
+    assert _lib.workspace_bytes_min(_lib.gemm_desc(128, 128, 128)) == 0
     d = _lib.conv2d_desc(256, 128, 28, 28, 128, 3, 3, pad=1)
     act = 256 * 28 * 28 * 128 * 2
     flt = 128 * 9 * 128 * 2
-    assert _lib.workspace_bytes(d) == (act + 1023) // 1024 * 1024 + (flt + 1023) // 1024 * 1024
+    assert _lib.workspace_bytes_min(d) == (act + 1023) // 1024 * 1024 + (flt + 1023) // 1024 * 1024
     # channel padding: activation to a multiple of 8, filter to a multiple of 64
     d = _lib.conv2d_desc(1, 3, 8, 8, 16, 3, 3, pad=1)
-    assert _lib.workspace_bytes(d) == 1024 + (16 * 9 * 64 * 2 + 1023) // 1024 * 1024
+    assert _lib.workspace_bytes_min(d) == 1024 + (16 * 9 * 64 * 2 + 1023) // 1024 * 1024
+    # the optional part: partial sums of a shared-out last round, one accumulator tile per CTA.  By
+    # default only where it clearly pays (7x7, C512 -> K512: 98 pair tiles on 74 pairs) ...
+    d = _lib.conv2d_desc(256, 512, 7, 7, 512, 3, 3, pad=1)
+    assert _lib.workspace_bytes(d) - _lib.workspace_bytes_min(d) == 148 * 128 * 256 * 4
+    d = _lib.conv2d_desc(256, 128, 28, 28, 128, 3, 3, pad=1)
+    assert _lib.workspace_bytes(d) == _lib.workspace_bytes_min(d)
+    assert _lib.workspace_bytes(_lib.gemm_desc(4096, 4096, 4096)) == 0
+    # ... and wherever a round is short when forced, never when forbidden
+    os.environ["AMOSB_TAIL_SHARING"] = "1"
+    try:
+        assert _lib.workspace_bytes(d) - _lib.workspace_bytes_min(d) == 148 * 256 * 128 * 4
+        big = _lib.gemm_desc(512, 4096, 4096)
+        assert _lib.workspace_bytes_min(big) == 0 and _lib.workspace_bytes(big) == 148 * 128 * 256 * 4
+        os.environ["AMOSB_NO_TAIL_SHARING"] = "1"
+        assert _lib.workspace_bytes(big) == 0
+    finally:
+        del os.environ["AMOSB_TAIL_SHARING"]
+        os.environ.pop("AMOSB_NO_TAIL_SHARING", None)
     bad = _lib.AmosbOpDesc()
     with pytest.raises(_lib.AmosbError):
         _lib.workspace_bytes(bad)

@@ -137,7 +137,7 @@ def test_recognise_float32_as_tf32(built_lib):
     # ... and so is NCHW (re-layout pass on 32-bit elements, channels padded to 4 / 32)
     d = _desc(ops.conv2d(1, 64, 8, 8, 64, 3, 3, 1, 1, 1, in_dtype="float32"))
     assert (d.kind, d.in_dtype) == (_lib.OP_CONV2D_NCHW, _lib.AMOSB_F32)
-    assert _lib.workspace_bytes(d) == (64 * 64 + 64 * 9 * 64) * 4
+    assert _lib.workspace_bytes_min(d) == (64 * 64 + 64 * 9 * 64) * 4
     # float64 tensors have no mapping: the reference's message, not a fallback
     with pytest.raises(_lib.AmosbError) as e:
         _desc(ops.conv2d(1, 64, 8, 8, 64, 3, 3, 1, 1, 1, in_dtype="float64", out_dtype="float64"))
@@ -159,7 +159,7 @@ def test_recognise_int8_conv_in_the_in_place_layouts(built_lib):
     d = _desc(ops.conv2d(1, 64, 8, 8, 64, 3, 3, 1, 1, 1, in_dtype="int8", out_dtype="int32"))
     assert (d.kind, d.in_dtype, d.out_dtype) == (_lib.OP_CONV2D_NCHW, _lib.AMOSB_S8, _lib.AMOSB_S32)
     # scratch: N*H*W pixels of 64 -> 64 channels, 64 filters of 9 taps x 128 padded channels, 1 byte each
-    assert _lib.workspace_bytes(d) == 64 * 64 + 64 * 9 * 128
+    assert _lib.workspace_bytes_min(d) == 64 * 64 + 64 * 9 * 128
 
 
 def test_recognise_float16_sums(built_lib):
@@ -217,7 +217,7 @@ def test_recognise_conv_nhwc(built_lib, cfg):
     assert (d.stride_h, d.stride_w, d.pad_h, d.pad_w, d.dil_h, d.dil_w) == \
         (st, st, pad, pad, dil, dil)
     assert d.conv_p == (H + 2 * pad - dil * (R - 1) - 1) // st + 1
-    assert _lib.workspace_bytes(d) == 0  # both operands are consumed where they lie
+    assert _lib.workspace_bytes_min(d) == 0  # both operands are consumed where they lie
     fused = _desc(ops.conv2d_nhwc_bias_relu(N, H, W, C, K, R, S, st, pad, dil))
     assert fused.kind == _lib.OP_CONV2D_NHWC
     assert fused.epilogue == _lib.EPI_ADD_VECTOR | _lib.EPI_RELU and fused.arg_c == 2
@@ -238,7 +238,7 @@ def test_recognise_conv_hwnc(built_lib, cfg):
         (N, C, H, W, K, R, S)
     assert (d.stride_h, d.pad_h, d.dil_h) == (st, pad, dil)
     assert d.conv_p == (H + 2 * pad - dil * (R - 1) - 1) // st + 1
-    assert _lib.workspace_bytes(d) == 0
+    assert _lib.workspace_bytes_min(d) == 0
     text = _lib.describe_plan(d)
     assert "conv-hwnc" in text and "umma_pair" not in text
     from amos_b200 import shard

@@ -23,7 +23,7 @@ def _run(desc, ins, shape):
     numel = int(np.prod(shape))
     buf = torch.full((numel + 2048,), 77, dtype=torch.int32, device=DEV)
     out = buf[1024:1024 + numel].view(shape)
-    assert _lib.workspace_bytes(desc) == 0
+    assert _lib.workspace_bytes_min(desc) == 0
     assert device.run(desc, [_t(x) for x in ins], [out]) == 1
     assert device.status_peek(0) == 0
     assert (buf[:1024] == 77).all() and (buf[1024 + numel:] == 77).all(), "wrote outside Out"

@@ -26,7 +26,7 @@ def _run(x, w, stride, pad, dil, out_dtype="float32", tile_n=0, cta_pair=0):
     d = _lib.conv2d_nhwc_desc(n, h, wd, c, k, r, s, stride, pad, dil,
                               out_dtype=_lib.DTYPE_CODES[out_dtype], tile_n=tile_n,
                               cta_pair=cta_pair)
-    assert _lib.workspace_bytes(d) == 0
+    assert _lib.workspace_bytes_min(d) == 0
     shape = (n, d.conv_p, d.conv_q, k)
     numel = int(np.prod(shape))
     tdt = device.CODE_TO_TORCH[d.out_dtype]
@@ -150,6 +150,18 @@ def test_full_size_layers(oracle, cfg):
     perm = torch.from_numpy(rng.permutation(n)).to(DEV)
     out2 = torch.empty_like(out)
     device.run(d, [tx[perm].contiguous(), tw], [out2])
+    if _lib.workspace_bytes(d) > _lib.workspace_bytes_min(d):
+        # the schedule shares out the tiles of its short last round (the 7x7 layer): the sums of an
+        # image that lands in such a tile are added in another order; bit for bit with whole tiles
+        import os
+        diff = (out2.double() - out[perm].double()).norm() / out.double().norm()
+        assert float(diff) <= 1e-5
+        os.environ["AMOSB_NO_TAIL_SHARING"] = "1"
+        try:
+            device.run(d, [tx, tw], [out])
+            device.run(d, [tx[perm].contiguous(), tw], [out2])
+        finally:
+            del os.environ["AMOSB_NO_TAIL_SHARING"]
     assert torch.equal(out2, out[perm])
 
 

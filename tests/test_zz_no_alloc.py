@@ -41,7 +41,7 @@ def _static_call(desc, x, w, out):
 def test_static_scratch_matches_caller_scratch_twice(oracle):
     rng = np.random.default_rng(99)
     desc = _lib.conv2d_desc(1, 64, 56, 56, 64, 3, 3, stride=1, pad=1)
-    assert 0 < _lib.workspace_bytes(desc) <= _lib.STATIC_SCRATCH_BYTES
+    assert 0 < _lib.workspace_bytes_min(desc) <= _lib.STATIC_SCRATCH_BYTES
     for call in range(2):
         x_np = rng.uniform(-1, 1, (1, 64, 56, 56)).astype(np.float16)
         w_np = rng.uniform(-1, 1, (64, 64, 3, 3)).astype(np.float16)
@@ -76,7 +76,7 @@ def test_static_scratch_second_shape_and_limits():
     assert torch.equal(got, ref)
     # beyond the built-in maximum: refused with a message, nothing launched
     big = _lib.conv2d_desc(256, 128, 28, 28, 128, 3, 3, stride=1, pad=1)
-    assert _lib.workspace_bytes(big) > _lib.STATIC_SCRATCH_BYTES
+    assert _lib.workspace_bytes_min(big) > _lib.STATIC_SCRATCH_BYTES
     xb = torch.zeros(256, 128, 28, 28, dtype=torch.float16, device=DEV)
     wb = torch.zeros(128, 128, 3, 3, dtype=torch.float16, device=DEV)
     ob = torch.full((256, 128, 28, 28), 5.0, dtype=torch.float32, device=DEV)
