@@ -710,7 +710,7 @@ def run_ours(args):
     name = args.workload
     w = WORKLOADS[name]
     sampler = ClockSampler(dev) if rank == 0 else None
-    need_i8 = w.get("dtype") == "s8" or not args.no_others
+    need_i8 = (w.get("dtype") == "s8" or not args.no_others) and not args.no_int8_peak
     int8_peak = measure_int8_library_peak(dev) if need_i8 else None
     if world > 1 and need_i8:
         # every rank measured its own GPU; the slowest one is the job's denominator
@@ -913,6 +913,9 @@ def main():
                          "workload lasts at least this long (0: one pass)")
     ap.add_argument("--no-others", action="store_true", help="skip the non-headline configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-int8-peak", action="store_true",
+                    help="skip measuring the int8 library peak (int8 rows then use 2 x the bf16 peak, "
+                         "stated); for runs under a profiler")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
