@@ -68,6 +68,7 @@ struct UmmaParams {
   // fused trailing element-wise stages, applied to the accumulator before the final cast:
   // out = cast(relu?(acc + addend?)).  The addend is either a vector indexed by the N column
   // (GEMM: j, conv: output channel) or a tensor of the output's shape.
+  int nchw_quads;       // NCHW output planes are whole 4-pixel groups and aligned: store 4 pixels at a time
   int epi_flags;        // kEpiAddVec | kEpiAddFull | kEpiRelu | kEpiAddRowVec (vector indexed by the row)
   int addend_f16;       // addend stored as fp16 (cast to the accumulator type before the add)
   const void* addend;
@@ -387,6 +388,42 @@ __device__ __forceinline__ void store_row_chunk(OutT* __restrict__ dst, const ui
   }
 }
 
+// NCHW store of a 32-column chunk when every image plane is a whole number of 4-pixel groups.
+// A thread holds one pixel (row) of 32 channels; groups of 4 lanes transpose 4 x 4 blocks among
+// themselves with shuffles, after which a lane holds 4 consecutive pixels of one channel and stores
+// them as one 16-byte (float32, int32) or 8-byte (float16) unit: a quarter of the store instructions
+// of the element-wise form, each of which the memory pipe takes as long to accept.
+// `quad_dst` points at the lane's own channel (chunk column lane & 3) and the first pixel of the
+// lane's 4-row group; `plane` is the distance between channel planes in elements.  All 32 lanes
+// must call; lanes whose group lies past the last row pass quad_ok = false.
+template <typename OutT>
+__device__ __forceinline__ void store_nchw_quads(OutT* __restrict__ quad_dst, long long plane,
+                                                 const uint32_t (&r)[32], int ncols_valid,
+                                                 uint32_t lane, bool quad_ok) {
+  const bool hi2 = (lane & 2u) != 0, hi1 = (lane & 1u) != 0;
+  const int my_col = static_cast<int>(lane & 3u);
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const uint32_t a0 = r[4 * b], a1 = r[4 * b + 1], a2 = r[4 * b + 2], a3 = r[4 * b + 3];
+    // 2 x 2 blocks change places between lanes i and i ^ 2 ...
+    const uint32_t t0 = __shfl_xor_sync(0xffffffffu, hi2 ? a0 : a2, 2);
+    const uint32_t t1 = __shfl_xor_sync(0xffffffffu, hi2 ? a1 : a3, 2);
+    const uint32_t b0 = hi2 ? t0 : a0, b1 = hi2 ? t1 : a1, b2 = hi2 ? a2 : t0, b3 = hi2 ? a3 : t1;
+    // ... then single elements between lanes i and i ^ 1
+    const uint32_t v0 = __shfl_xor_sync(0xffffffffu, hi1 ? b0 : b1, 1);
+    const uint32_t v1 = __shfl_xor_sync(0xffffffffu, hi1 ? b2 : b3, 1);
+    const uint32_t c0 = hi1 ? v0 : b0, c1 = hi1 ? b1 : v0, c2 = hi1 ? v1 : b2, c3 = hi1 ? b3 : v1;
+    if (quad_ok && 4 * b + my_col < ncols_valid) {
+      OutT* dst = quad_dst + static_cast<long long>(4 * b) * plane;
+      if constexpr (sizeof(OutT) == 4) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(c0, c1, c2, c3);
+      } else {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_half2(c0, c1), pack_half2(c2, c3));
+      }
+    }
+  }
+}
+
 // A_MN_MAJOR: A is given as [K][M] (the `te` text indexes it A[k, i]) and consumed in place as an
 // MN-major operand, in chunks of 128 bytes of M like an MN-major B.  GEMM mode, MT = 1 only.
 template <int KIND, int BN, bool B_MN_MAJOR, int MODE, typename OutT, bool EPI_TMA, int MT = 1,
@@ -632,7 +669,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           const uint32_t fb = full_bar(stage);
 #ifdef AMOSB_ROLE_CYCLES
           const bool dbg_no_a = (p.dbg_skip & 1) != 0, dbg_no_b = (p.dbg_skip & 2) != 0;
-          mbar_arrive_expect_tx(fb, (dbg_no_a ? 0 : MT * kATileBytes) +
+          mbar_arrive_expect_tx(fb, ((dbg_no_a || MODE == kModeConvPw) ? 0 : MT * kATileBytes) +
                                         (dbg_no_b ? 0 : Cfg::kBTileBytes));
 #define AMOSB_DBG_A if (!dbg_no_a)
 #define AMOSB_DBG_B if (!dbg_no_b)
@@ -1001,6 +1038,8 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         });
       } else {
         OutT* row_ptr = nullptr;
+        OutT* quad_ptr = nullptr;  // NCHW in 4-pixel units: this lane's channel and 4-row group
+        bool quad_ok = false;
         if constexpr (!kNchwOut) {
           row_ptr = out + static_cast<long long>(b) * p.c_batch_stride +
                     static_cast<long long>(orow) * p.ldc;
@@ -1008,6 +1047,13 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           const int n_img = row / p.PQ;
           const int pq = row - n_img * p.PQ;
           row_ptr = out + (static_cast<long long>(n_img) * p.N) * p.PQ + pq;
+          if (p.nchw_quads) {
+            const int qrow = row0 + static_cast<int>(lane & ~3u);
+            const int q_img = qrow / p.PQ;
+            quad_ok = qrow < p.M;
+            quad_ptr = out + (static_cast<long long>(q_img) * p.N + (lane & 3u)) * p.PQ +
+                       (qrow - q_img * p.PQ);
+          }
         }
         run_chunks(valid_chunks, [&](uint32_t(&r)[32], int c) {
           const int col0 = n_blk * BN + c * 32;
@@ -1029,6 +1075,13 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                                  ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
                                  : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
             apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row_ok, fp, stride);
+          }
+          if constexpr (kNchwOut) {
+            if (p.nchw_quads) {  // warp-uniform
+              store_nchw_quads<OutT>(quad_ptr + static_cast<long long>(col0) * p.PQ, p.PQ, r,
+                                     ncols_valid, lane, quad_ok);
+              return;
+            }
           }
           if (row_ok) {
             if constexpr (!kNchwOut) {

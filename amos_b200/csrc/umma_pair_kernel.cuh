@@ -487,6 +487,8 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         });
       } else {
         OutT* row_ptr = nullptr;
+        OutT* quad_ptr = nullptr;  // NCHW in 4-pixel units: this lane's channel and 4-row group
+        bool quad_ok = false;
         if constexpr (MODE != kModeConv) {
           row_ptr = out + static_cast<long long>(b) * p.c_batch_stride +
                     static_cast<long long>(row) * p.ldc;
@@ -494,6 +496,13 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int n_img = row / p.PQ;
           const int pq = row - n_img * p.PQ;
           row_ptr = out + (static_cast<long long>(n_img) * p.N) * p.PQ + pq;
+          if (p.nchw_quads) {
+            const int qrow = row0 + static_cast<int>(lane & ~3u);
+            const int q_img = qrow / p.PQ;
+            quad_ok = qrow < p.M;
+            quad_ptr = out + (static_cast<long long>(q_img) * p.N + (lane & 3u)) * p.PQ +
+                       (qrow - q_img * p.PQ);
+          }
         }
         run_chunks(valid_chunks, [&](uint32_t(&r)[32], int c) {
           const int col0 = n_blk * BN + n_off + c * 32;
@@ -515,6 +524,13 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                  ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
                                  : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
             apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row < p.M, fp, stride);
+          }
+          if constexpr (MODE == kModeConv) {
+            if (p.nchw_quads) {  // warp-uniform
+              store_nchw_quads<OutT>(quad_ptr + static_cast<long long>(col0) * p.PQ, p.PQ, r,
+                                     ncols_valid, lane, quad_ok);
+              return;
+            }
           }
           if (row < p.M) {
             if constexpr (MODE != kModeConv) {

@@ -512,6 +512,32 @@ def test_conv2d_tile_variants_and_fp16_out(oracle, tile_n):
     assert np.array_equal(got16, got.astype(np.float16))
 
 
+@pytest.mark.parametrize("cfg", [
+    # n, c, h, w, k, r, pad, cta_pair: planes of 4n pixels that tiles cut across, ragged channels
+    (5, 64, 10, 10, 300, 3, 1, 1), (5, 64, 10, 10, 300, 3, 1, 2), (3, 136, 14, 14, 72, 1, 0, 0),
+    (40, 72, 6, 6, 264, 3, 1, 0), (2, 64, 9, 9, 80, 3, 1, 0)])
+@pytest.mark.parametrize("out_dtype", ["float32", "float16"])
+def test_conv2d_nchw_four_pixel_stores_match_element_stores(oracle, cfg, out_dtype):
+    """The NCHW epilogue that stores 4 pixels per lane (after a transposition among lanes) writes
+    exactly what the element-wise epilogue writes; planes that are not whole 4-pixel groups (9x9)
+    keep the element-wise form either way."""
+    n, c, h, w, k, r, pad, cta_pair = cfg
+    rng = np.random.default_rng(n * 1000 + k)
+    x = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float16)
+    wt = rng.normal(0, 0.05, (k, c, r, r)).astype(np.float16)
+    got = {}
+    for mode in ("0", "1"):
+        os.environ["AMOSB_NCHW_QUADS"] = mode
+        try:
+            got[mode] = _run_conv(x, wt, 1, pad, 1, out_dtype=out_dtype, cta_pair=cta_pair,
+                                  launches_expected=1 if r == 1 else 2)
+        finally:
+            del os.environ["AMOSB_NCHW_QUADS"]
+    assert np.array_equal(got["0"], got["1"])
+    ref = oracle.c_conv2d_nchw(x, wt, 1, pad, 1, "te_llvm")
+    assert oracle.rel_l2(got["1"].astype(np.float32), ref) <= (TOL_TE_LLVM if out_dtype == "float32" else 1e-3)
+
+
 # ------------------------------------------------------------------------------ golden fixtures
 def test_golden_reference_helpers(golden_dir):
     g = np.load(os.path.join(golden_dir, "ref_topi_conv2d_nchw.npz"))
