@@ -766,8 +766,8 @@ static void plan_for_desc(const AmosbOpDesc& d, int sm_count, int* bn, bool* pai
   const long long kblocks = conv ? d.conv_r * d.conv_s * ((d.conv_c + kelems - 1) / kelems)
                                  : (d.k + kelems - 1) / kelems;
   // A indexed [k,i] runs on single-CTA 128-row tiles only; HWNC on single-CTA tiles (128 or 256 rows)
-  // and so do float32 (tf32) operands and int8 conv
-  const bool single_only = (!conv && d.trans_a) || d.in_dtype == AMOSB_F32 ||
+  // and so do float32 (tf32) and int8 convolutions
+  const bool single_only = (!conv && d.trans_a) || (conv && d.in_dtype == AMOSB_F32) ||
                            (conv && d.in_dtype == AMOSB_S8);
   int pair_mode = single_only ? 1 : d.cta_pair;
   if (d.kind == AMOSB_OP_CONV2D_HWNC && !single_only && (pair_mode == 0 || pair_mode == 2))
@@ -919,12 +919,11 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
       set_error("float32 (tf32) inputs accumulate into and write float32");
       return AMOSB_ERR_UNSUPPORTED;
     }
-    // single-CTA 128-row tiles only
-    if (pair_mode == 2 || pair_mode == 3) {
+    // single-CTA 128-row tiles and CTA pairs; no tall tiles
+    if (pair_mode == 3) {
       set_error("cta_pair=%d is not available for float32 (tf32) inputs", pair_mode);
       return AMOSB_ERR_UNSUPPORTED;
     }
-    pair_mode = 1;
   }
   const int es = is_i8 ? 1 : is_tf32 ? 4 : 2;
   const int elems128 = 128 / es;
@@ -1030,6 +1029,8 @@ static int run_gemm_core(DeviceState* st, int in_dtype, int out_dtype, bool tran
                                       static_cast<size_t>(kBlockM) * bn, ws, ws_bytes);
     if (is_i8)
       return dispatch_pair_gemm<1, int32_t>(trans_b, epi_tma, bn, tmA, tmB, tmC, p, npairs, stream);
+    if (is_tf32)
+      return dispatch_pair_gemm<2, float>(trans_b, epi_tma, bn, tmA, tmB, tmC, p, npairs, stream);
     if (out_dtype == AMOSB_F32)
       return dispatch_pair_gemm<0, float>(trans_b, epi_tma, bn, tmA, tmB, tmC, p, npairs, stream);
     if (out_dtype == AMOSB_F16)

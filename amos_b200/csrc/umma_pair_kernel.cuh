@@ -37,8 +37,9 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmC, const UmmaParams p) {
   using Cfg = PairConfig<BN, EPI_TMA>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int kElemsPer128B = (KIND == 0) ? 64 : 128;
-  constexpr int kUmmaKRows = (KIND == 0) ? 16 : 32;
+  constexpr int kElemsPer128B = (KIND == 0) ? 64 : (KIND == 1) ? 128 : 32;
+  constexpr int kUmmaKRows = (KIND == 0) ? 16 : (KIND == 1) ? 32 : 8;
+  static_assert(KIND != 2 || MODE == kModeGemm, "float32 (tf32) pairs: GEMM only");
   constexpr int kMmaPerStage = 4;
   constexpr uint32_t kBChunkBytes = kElemsPer128B * 128;
   constexpr int kBChunksPerCta = (BN / 2) / kElemsPer128B;  // MN-major chunks this CTA loads
@@ -283,10 +284,13 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #endif
           constexpr int kAStep = 32 >> 4;
           constexpr int kBStep = B_MN_MAJOR ? (kUmmaKRows * 128) >> 4 : 32 >> 4;
+          // MN-major operands of 32-bit elements lie in the 128-byte swizzle with 32-byte units
+          constexpr uint32_t kHiMn =
+              KIND == 2 ? smem_desc_hi_sw128_base32(512) : smem_desc_hi_sw128(1024);
           umma_kblock4<KIND, true, kAStep, kBStep>(tmem_d, smem_desc_lo(sA, 16),
                                                    smem_desc_lo(sB, B_MN_MAJOR ? kBChunkBytes : 16),
                                                    smem_desc_hi_sw128(1024),
-                                                   smem_desc_hi_sw128(1024), idesc,
+                                                   B_MN_MAJOR ? kHiMn : smem_desc_hi_sw128(1024), idesc,
                                                    kb != sg.kb_begin ? 1u : 0u);
 #ifdef AMOSB_ROLE_CYCLES
           const long long rc_t3 = clock64();

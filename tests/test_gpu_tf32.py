@@ -67,6 +67,32 @@ def test_gemm_tf32(oracle, shape, trans_b):
     assert np.array_equal(got_t, got)
 
 
+@pytest.mark.parametrize("shape", [(512, 256, 64), (1000, 520, 264), (300, 136, 100), (2048, 1024, 512)])
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("tile_n", [0, 128, 256])
+def test_gemm_tf32_cta_pairs(oracle, shape, trans_b, tile_n):
+    """CTA-pair tiles (256 rows, tcgen05.mma.cta_group::2.kind::tf32): the same products in the same
+    order as the single-CTA tiles, ragged edges and partial last rounds included."""
+    m, n, k = shape
+    rng = np.random.default_rng(7 * m + n + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, k) if trans_b else (k, n)).astype(np.float32)
+    pair = _gemm(a, b, trans_b=trans_b, tile_n=tile_n, cta_pair=2)
+    single = _gemm(a, b, trans_b=trans_b, tile_n=tile_n, cta_pair=1)
+    assert np.array_equal(pair, single)
+    _check(oracle, pair, a, b, trans_b=trans_b)
+
+
+def test_batched_gemm_tf32_cta_pairs(oracle):
+    rng = np.random.default_rng(11)
+    a = rng.uniform(-1, 1, (3, 300, 72)).astype(np.float32)
+    b = rng.uniform(-1, 1, (3, 72, 264)).astype(np.float32)
+    pair = _gemm(a, b, cta_pair=2)
+    assert np.array_equal(pair, _gemm(a, b, cta_pair=1))
+    for i in range(3):
+        _check(oracle, pair[i], a[i], b[i])
+
+
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 def test_gemm_tf32_tile_widths(oracle, tile_n):
     rng = np.random.default_rng(tile_n)
@@ -149,12 +175,12 @@ def test_full_size_gemm_tf32(oracle):
 
 def test_tf32_limits():
     a = torch.zeros(64, 64, dtype=torch.float32, device=DEV)
-    # narrowing output, CTA-pair and tall tiles: refused, not emulated
+    # narrowing output and tall tiles: refused, not emulated
     d = _lib.gemm_desc(64, 64, 64, in_dtype=_lib.AMOSB_F32, out_dtype=_lib.AMOSB_F16)
     with pytest.raises(_lib.AmosbError) as e:
         device.run(d, [a, a.clone()], [torch.zeros(64, 64, dtype=torch.float16, device=DEV)])
     assert e.value.code == _lib.AMOSB_ERR_UNSUPPORTED
-    for pin in (2, 3):
+    for pin in (3,):
         d = _lib.gemm_desc(512, 256, 64, in_dtype=_lib.AMOSB_F32, cta_pair=pin)
         x = torch.zeros(512, 64, dtype=torch.float32, device=DEV)
         y = torch.zeros(64, 256, dtype=torch.float32, device=DEV)
