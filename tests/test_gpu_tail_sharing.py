@@ -85,6 +85,21 @@ def test_gemm_int8_is_bit_exact(oracle, tile_n, cta_pair):
     assert np.array_equal(got, oracle.c_gemm(a, b, "exact"))
 
 
+@pytest.mark.parametrize("tile_n,cta_pair", [(256, 1), (128, 1), (256, 2), (128, 2)])
+def test_gemm_tf32_single_cta_and_pairs(oracle, tile_n, cta_pair):
+    m, n, k = 1100, 520, 520  # 17 k-blocks of 32, the last one ragged
+    rng = np.random.default_rng(31 + tile_n + cta_pair)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    d = _lib.gemm_desc(m, n, k, in_dtype=_lib.AMOSB_F32, tile_n=tile_n, cta_pair=cta_pair)
+    ins = [_t(a), _t(b)]
+    got = _run(d, ins, (m, n), True)
+    whole = _run(d, ins, (m, n), False)
+    assert oracle.rel_l2(got, oracle.np_gemm_f32(a, b, "tf32_rne")) <= 2e-5
+    assert oracle.rel_l2(got, whole) <= TOL_REORDER
+    assert np.array_equal(got, _run(d, ins, (m, n), True))
+
+
 def test_round_of_whole_tiles_after_the_shares(oracle):
     """More tiles than CTAs: shares first, then whole tiles on the same accumulators."""
     m, n, k = 128 * 20, 2048, 2048  # 160 tiles of 128 x 256, 32 k-blocks: 12 tiles shared out
