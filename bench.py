@@ -597,6 +597,30 @@ def roofline_for(desc_full, ops, byts, ms_per_step, n_gpus, peaks, peaks_kind, l
             "peak_source": f"hbm_gbs of {peaks_kind}"}
 
 
+def same_size_copy_us(total_bytes, dev, reps=20):
+    """Time of a plain device-to-device copy that moves `total_bytes` (half read, half written), on
+    four buffer pairs in rotation so that L2 serves nothing: what this box's memory system gives a
+    kernel of that size.  Small transfers stay far below the large-copy rate that is the roofline
+    denominator (a 64 MB copy runs at about half of it), so HBM-bound configurations carry this
+    figure beside their fraction.  None if the buffers would not be small beside the GPU's memory."""
+    import torch
+    half = int(total_bytes // 2) // 16 * 16
+    if half <= 0 or half * 8 > (8 << 30):
+        return None
+    src = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(4)]
+    dst = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(4)]
+    for i in range(4):
+        dst[i].copy_(src[i])
+    torch.cuda.synchronize(dev)
+    beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    beg.record()
+    for i in range(reps):
+        dst[i % 4].copy_(src[i % 4])
+    end.record()
+    end.synchronize()
+    return beg.elapsed_time(end) / reps * 1e3
+
+
 def config_for(name, world, scaling):
     """The `config` object of the JSON line; both arms print the same one."""
     w = WORKLOADS[name]
@@ -766,6 +790,11 @@ def run_ours(args):
                              "roofline_frac": rf["frac"], "kernels_per_step": r["launches_per_step"]}
             if world > 1:
                 others[other]["shard_parity"] = bool(o_red["shard_ok"])
+            elif rf["bound"] == "hbm":
+                cp_us = same_size_copy_us(o_red["bytes_local"], dev)
+                if cp_us:
+                    others[other]["copy_of_same_bytes_us"] = cp_us
+                    others[other]["frac_of_same_size_copy"] = cp_us / (per * 1e3)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
