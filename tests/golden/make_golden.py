@@ -1,7 +1,7 @@
 """Generate the committed golden fixtures of tests/golden/.
 
-Run once, in an environment that has the reference checkout (default /root/reference, override
-with AMOS_REFERENCE):  ``python tests/golden/make_golden.py``
+Run once, in an environment that has the reference checkout (by default a directory `reference`
+beside this repository; AMOS_REFERENCE overrides it):  ``python tests/golden/make_golden.py``
 
 Two families of fixtures are written:
 
@@ -33,7 +33,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("AMOS_REFERENCE", "/root/reference")
+REF = os.environ.get("AMOS_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def _load_reference_helpers():

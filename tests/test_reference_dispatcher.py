@@ -17,7 +17,9 @@ from amos_b200 import _lib, tvm
 from amos_b200 import auto_tensorize as at
 import ops
 
-REF_FILE = os.path.join(os.environ.get("AMOS_REFERENCE", "/root/reference"),
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the checkout is looked for beside this repository unless AMOS_REFERENCE names it
+REF_FILE = os.path.join(os.environ.get("AMOS_REFERENCE", os.path.join(os.path.dirname(_REPO), "reference")),
                         "python/tvm/tensor_graph/core/auto_schedule/auto_schedule.py")
 WANTED = ("auto_tensorize_cuda", "AutoTensorizeContext")
 
