@@ -198,15 +198,15 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           } else {
-            tma_load_im2col_4d_pair(sA, &tmA, fb, cc * 64, cw, ch, cn,
+            tma_load_im2col_4d_pair(sA, &tmA, fb, cc * kElemsPer128B, cw, ch, cn,
                                     static_cast<uint16_t>(fs * p.dil_w),
                                     static_cast<uint16_t>(fr * p.dil_h));
             if constexpr (MODE == kModeConv) {
               for (int j = 0; j * 64 < half; ++j) {
-                tma_load_2d_pair(sB + j * 64 * 128, &tmB, fb, kabs * 64, n_half0 + j * 64);
+                tma_load_2d_pair(sB + j * 64 * 128, &tmB, fb, kabs * kElemsPer128B, n_half0 + j * 64);
               }
             } else {
-              const int brow = (fr * p.S + fs) * p.conv_C + cc * 64;
+              const int brow = (fr * p.S + fs) * p.conv_C + cc * kElemsPer128B;
               for (int j = 0; j * kElemsPer128B < half; ++j) {
                 tma_load_3d_pair(sB + j * kBChunkBytes, &tmB, fb, n_half0 + j * kElemsPer128B,
                                  brow, 0);

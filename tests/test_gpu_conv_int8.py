@@ -58,6 +58,26 @@ def test_conv2d_nhwc_int8(oracle, cfg, tile_n):
         assert not np.array_equal(got, oracle.np_conv2d_nhwc(x, wt, st, pad, dil, "te_llvm"))
 
 
+@pytest.mark.parametrize("cfg", [
+    # N, H, W, C, K, R, S, stride, pad, dil: CTA-pair tiles are 256 pixels x 256 filters
+    (5, 15, 15, 160, 272, 3, 3, 2, 1, 1),    # ragged channel chunk, ragged second filter tile
+    (5, 14, 14, 128, 256, 3, 3, 1, 1, 1),    # 980 pixels: four pair tiles, the last one ragged
+    (2, 10, 10, 256, 304, 1, 1, 1, 0, 1),
+    (40, 14, 14, 128, 512, 3, 3, 1, 1, 1),   # 62 pair tiles: most of the 74 pairs busy
+])
+def test_conv2d_nhwc_int8_cta_pairs(oracle, cfg):
+    """int8 NHWC on CTA pairs (tcgen05.mma.cta_group::2.kind::i8): bit for bit the oracle's sums."""
+    n, h, w, c, k, r, s, st, pad, dil = cfg
+    rng = np.random.default_rng(n * 10 + k)
+    x = rng.integers(-128, 128, (n, h, w, c), dtype=np.int8)
+    wt = rng.integers(-128, 128, (r, s, c, k), dtype=np.int8)
+    d = _lib.conv2d_nhwc_desc(n, h, w, c, k, r, s, st, pad, dil, in_dtype=_lib.AMOSB_S8,
+                              tile_n=256, cta_pair=2)
+    assert "umma_pair" in _lib.describe_plan(d)
+    got = _run(d, [x, wt], (n, d.conv_p, d.conv_q, k))
+    assert np.array_equal(got, oracle.np_conv2d_nhwc(x, wt, st, pad, dil, "exact"))
+
+
 @pytest.mark.parametrize("cfg", [(6, 6, 128, 128, 128, 3, 3, 1, 1, 1),
                                  (5, 7, 256, 48, 144, 3, 3, 2, 1, 1),
                                  (4, 4, 128, 256, 48, 1, 1, 1, 0, 1)])
@@ -127,7 +147,8 @@ def test_limits():
         device.run(_lib.conv2d_nhwc_desc(1, 8, 8, 24, 16, 3, 3, pad=1, in_dtype=_lib.AMOSB_S8),
                    [x, w], [y])
     assert e.value.code == _lib.AMOSB_ERR_UNSUPPORTED
-    d = _lib.conv2d_nhwc_desc(4, 8, 8, 32, 128, 3, 3, pad=1, in_dtype=_lib.AMOSB_S8, cta_pair=2)
+    # tall tiles are not built for int8 (CTA pairs are, for NHWC)
+    d = _lib.conv2d_nhwc_desc(4, 8, 8, 32, 128, 3, 3, pad=1, in_dtype=_lib.AMOSB_S8, cta_pair=3)
     with pytest.raises(_lib.AmosbError) as e:
         device.run(d, [torch.zeros(4, 8, 8, 32, dtype=torch.int8, device=DEV),
                        torch.zeros(3, 3, 32, 128, dtype=torch.int8, device=DEV)],
