@@ -766,9 +766,10 @@ static void plan_for_desc(const AmosbOpDesc& d, int sm_count, int* bn, bool* pai
   const long long kblocks = conv ? d.conv_r * d.conv_s * ((d.conv_c + kelems - 1) / kelems)
                                  : (d.k + kelems - 1) / kelems;
   // A indexed [k,i] runs on single-CTA 128-row tiles only; HWNC on single-CTA tiles (128 or 256 rows)
-  // and so do float32 (tf32) convolutions and int8 convolutions other than NHWC
-  const bool single_only = (!conv && d.trans_a) || (conv && d.in_dtype == AMOSB_F32) ||
-                           (conv && d.in_dtype == AMOSB_S8 && d.kind != AMOSB_OP_CONV2D_NHWC);
+  // and so do float32 (tf32) and int8 convolutions other than NHWC
+  const bool single_only =
+      (!conv && d.trans_a) ||
+      (conv && (d.in_dtype == AMOSB_F32 || d.in_dtype == AMOSB_S8) && d.kind != AMOSB_OP_CONV2D_NHWC);
   int pair_mode = single_only ? 1 : d.cta_pair;
   if (d.kind == AMOSB_OP_CONV2D_HWNC && !single_only && (pair_mode == 0 || pair_mode == 2))
     pair_mode = 4;
@@ -1490,9 +1491,9 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     set_error("int8 conv2d writes int32");
     return AMOSB_ERR_UNSUPPORTED;
   }
-  // CTA pairs: float16 / bfloat16 and int8 NHWC; tall tiles: float16 / bfloat16 only
-  if ((is_tf32 && (d.cta_pair == 2 || d.cta_pair == 3)) ||
-      (is_i8 && (d.cta_pair == 3 || (d.cta_pair == 2 && d.kind != AMOSB_OP_CONV2D_NHWC)))) {
+  // CTA pairs: float16 / bfloat16, and for NHWC also int8 and float32; tall tiles: float16 / bfloat16 only
+  if ((is_tf32 || is_i8) &&
+      (d.cta_pair == 3 || (d.cta_pair == 2 && d.kind != AMOSB_OP_CONV2D_NHWC))) {
     set_error("cta_pair=%d is not available for float32 (tf32) or int8 conv2d", d.cta_pair);
     return AMOSB_ERR_UNSUPPORTED;
   }
@@ -1616,6 +1617,14 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
                                        static_cast<size_t>(kBlockM) * bn, workspace, workspace_bytes);
     if (epi_tma) return dispatch_pair_bn<1, true, kModeConvNhwc, int32_t, true>(bn, tmA, tmB, tmC, p, npairs8, stream);
     return dispatch_pair_bn<1, true, kModeConvNhwc, int32_t, false>(bn, tmA, tmB, tmC, p, npairs8, stream);
+  }
+  if (is_tf32 && pairs) {
+    p.tiles_m = (int)((Mtot + 2 * kBlockM - 1) / (2 * kBlockM));
+    p.num_tiles = (int)(((Mtot + 2 * kBlockM - 1) / (2 * kBlockM)) * ((Kout + bn - 1) / bn));
+    const int npairs32 = setup_schedule(&p, st, device, st->sm_count / 2, 2,
+                                        static_cast<size_t>(kBlockM) * bn, workspace, workspace_bytes);
+    if (epi_tma) return dispatch_pair_bn<2, true, kModeConvNhwc, float, true>(bn, tmA, tmB, tmC, p, npairs32, stream);
+    return dispatch_pair_bn<2, true, kModeConvNhwc, float, false>(bn, tmA, tmB, tmC, p, npairs32, stream);
   }
   if (is_i8) {
     const int grid8 = setup_schedule(&p, st, device, st->sm_count, 1,

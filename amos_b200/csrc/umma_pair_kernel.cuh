@@ -39,7 +39,8 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPer128B = (KIND == 0) ? 64 : (KIND == 1) ? 128 : 32;
   constexpr int kUmmaKRows = (KIND == 0) ? 16 : (KIND == 1) ? 32 : 8;
-  static_assert(KIND != 2 || MODE == kModeGemm, "float32 (tf32) pairs: GEMM only");
+  static_assert(KIND != 2 || MODE == kModeGemm || MODE == kModeConvNhwc,
+                "float32 (tf32) pairs: GEMM and NHWC convolution");
   constexpr int kMmaPerStage = 4;
   constexpr uint32_t kBChunkBytes = kElemsPer128B * 128;
   constexpr int kBChunksPerCta = (BN / 2) / kElemsPer128B;  // MN-major chunks this CTA loads

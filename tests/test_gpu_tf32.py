@@ -249,6 +249,32 @@ def test_conv2d_nhwc_tf32(oracle, cfg):
         <= TOL_REFERENCE
 
 
+@pytest.mark.parametrize("cfg", [
+    (5, 15, 15, 36, 272, 3, 3, 2, 1, 1),     # ragged channel chunk, ragged second filter tile
+    (5, 14, 14, 32, 256, 3, 3, 1, 1, 1),     # 980 pixels: four pair tiles, the last one ragged
+    (2, 10, 10, 100, 304, 1, 1, 1, 0, 1),
+    (40, 14, 14, 32, 512, 3, 3, 1, 1, 1),    # 62 pair tiles
+])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_conv2d_nhwc_tf32_cta_pairs(oracle, cfg, tile_n):
+    """float32 NHWC on CTA pairs: the same products in the same order as the single-CTA tiles."""
+    n, h, w, c, k, r, s, st, pad, dil = cfg
+    rng = np.random.default_rng(n * 10 + k)
+    x = rng.uniform(-1, 1, (n, h, w, c)).astype(np.float32)
+    wt = rng.normal(0, 0.05, (r, s, c, k)).astype(np.float32)
+    outs = []
+    for pair in (2, 1):
+        d = _lib.conv2d_nhwc_desc(n, h, w, c, k, r, s, st, pad, dil, tile_n=tile_n, cta_pair=pair)
+        d.in_dtype = _lib.AMOSB_F32
+        assert ("umma_pair" in _lib.describe_plan(d)) == (pair == 2)
+        out = torch.full((n, d.conv_p, d.conv_q, k), float("nan"), dtype=torch.float32, device=DEV)
+        assert device.run(d, [_t(x), _t(wt)], [out]) == 1
+        assert device.status_peek(0) == 0
+        outs.append(out.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])
+    assert oracle.rel_l2(outs[0], oracle.np_conv2d_nhwc_f32(x, wt, st, pad, dil, HW_MODE)) <= TOL_HW
+
+
 @pytest.mark.parametrize("cfg", [(6, 6, 128, 32, 32, 3, 3, 1, 1, 1), (5, 7, 256, 36, 72, 3, 3, 2, 1, 1),
                                  (4, 4, 128, 64, 40, 1, 1, 1, 0, 1)])
 def test_conv2d_hwnc_tf32(oracle, cfg):
@@ -279,8 +305,8 @@ def test_conv2d_tf32_limits_and_front_end(oracle):
     import ops
     from amos_b200 import tvm
     from amos_b200.tvm import auto_tensorize as at
-    # CTA-pair / tall tiles are not built for float32 tensors
-    d = _lib.conv2d_nhwc_desc(4, 8, 8, 32, 128, 3, 3, pad=1, in_dtype=_lib.AMOSB_F32, cta_pair=2)
+    # tall tiles are not built for float32 tensors (CTA pairs are, for NHWC)
+    d = _lib.conv2d_nhwc_desc(4, 8, 8, 32, 128, 3, 3, pad=1, in_dtype=_lib.AMOSB_F32, cta_pair=3)
     with pytest.raises(_lib.AmosbError) as e:
         device.run(d, [torch.zeros(4, 8, 8, 32, dtype=torch.float32, device=DEV),
                        torch.zeros(3, 3, 32, 128, dtype=torch.float32, device=DEV)],
