@@ -744,8 +744,23 @@ int amosb_describe_plan(const AmosbOpDesc* desc, int device, char* buf, int buf_
                  dtype_name(desc->in_dtype), dtype_name(desc->out_dtype), fam, bn, rows, bn, stages,
                  tall ? 2 * bn : bn, tiles, tiles < slots ? tiles : slots,
                  pair ? "CTA pairs" : "CTAs");
+  } else if (desc->kind == AMOSB_OP_CONV2D_HWNC && desc->conv_n <= 64 && desc->stride_w == 1 &&
+             getenv("AMOSB_HWNC_NO_PACKING") == nullptr) {
+    int nbox = 8;
+    while (nbox < desc->conv_n) nbox *= 2;
+    const int group = 128 / nbox;
+    const long long m = desc->conv_p * ((desc->conv_q + group - 1) / group) * 128;
+    const long long tiles = ((m + rows - 1) / rows) * ((desc->conv_k + bn - 1) / bn);
+    n = snprintf(buf, buf_len,
+                 "plan conv2d_hwnc %s->%s, operands in place (no re-layout, no workspace): [1] "
+                 "%s<%s,BN=%d,conv-hwnc> tile %dx%dx%d = %d consecutive pixels of an output row x %d "
+                 "images per accumulator, %d smem stages, tiled TMA A {%d channels, %d images, %d "
+                 "pixels} under each filter tap + MN-major TMA B (RSCK as [R*S*C][K]), TMA-store "
+                 "epilogue, %lld tiles on %lld CTAs",
+                 dtype_name(desc->in_dtype), dtype_name(desc->out_dtype), fam, ck, bn, rows, bn, cbk,
+                 group, nbox, stages, cbk, nbox, group, tiles, tiles < slots ? tiles : slots);
   } else if (desc->kind == AMOSB_OP_CONV2D_HWNC) {
-    const long long m = desc->conv_n * desc->conv_p * desc->conv_q;
+    const long long m = ((desc->conv_n + 127) / 128) * 128 * desc->conv_p * desc->conv_q;
     const long long tiles = ((m + rows - 1) / rows) * ((desc->conv_k + bn - 1) / bn);
     n = snprintf(buf, buf_len,
                  "plan conv2d_hwnc %s->%s, operands in place (no re-layout, no workspace): [1] "

@@ -150,11 +150,13 @@ static int encode_tiled_3d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_byt
 }
 
 // HWNC activation as {C, N, W, H}: boxes of 128 bytes of channels x 128 images of one input pixel.
+// With fewer than 128 images a box is `nbox` images x `group` consecutive input pixels of a row.
 static int encode_tiled_hwnc(CUtensorMap* tm, CUtensorMapDataType dt, uint64_t es, void* base,
-                             uint64_t c, uint64_t n, uint64_t w, uint64_t h) {
+                             uint64_t c, uint64_t n, uint64_t w, uint64_t h, uint32_t nbox = kBlockM,
+                             uint32_t group = 1) {
   cuuint64_t dims[4] = {c, n, w, h};
   cuuint64_t strides[3] = {c * es, n * c * es, w * n * c * es};
-  cuuint32_t box[4] = {(cuuint32_t)(128 / es), (cuuint32_t)kBlockM, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / es), nbox, group, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = g_encode_tiled(tm, dt, 4, base, dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -163,6 +165,28 @@ static int encode_tiled_hwnc(CUtensorMap* tm, CUtensorMapDataType dt, uint64_t e
     set_error("cuTensorMapEncodeTiled(hwnc) failed with %d (C %llu N %llu W %llu H %llu)", (int)r,
               (unsigned long long)c, (unsigned long long)n, (unsigned long long)w,
               (unsigned long long)h);
+    return AMOSB_ERR_CUDA;
+  }
+  return AMOSB_OK;
+}
+
+// HWNC output [P][Q][N][K] as {K, N, Q, P}: a store box is 128 bytes of K x 32 rows, the rows being
+// `nbox` images x 32 / nbox consecutive pixels of an output row (32 images of one pixel when the
+// image count is 32 or more).  Images past N and pixels past Q are dropped by the store engine.
+static int encode_store_hwnc(CUtensorMap* tm, CUtensorMapDataType dt, uint64_t ob, void* base,
+                             uint64_t k, uint64_t n, uint64_t q, uint64_t p, uint32_t nbox) {
+  cuuint64_t dims[4] = {k, n, q, p};
+  cuuint64_t strides[3] = {k * ob, n * k * ob, q * n * k * ob};
+  const uint32_t imgs = nbox < 32 ? nbox : 32;
+  cuuint32_t box[4] = {(cuuint32_t)(128 / ob), imgs, 32 / imgs, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode_tiled(tm, dt, 4, base, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled(hwnc output) failed with %d (K %llu N %llu Q %llu P %llu)",
+              (int)r, (unsigned long long)k, (unsigned long long)n, (unsigned long long)q,
+              (unsigned long long)p);
     return AMOSB_ERR_CUDA;
   }
   return AMOSB_OK;
@@ -1525,12 +1549,22 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   // HWNC: a tile is one output pixel x 128 images; other image counts are padded per pixel (the
   // padding images load as zeros and are not stored)
   const long long Npad = hwnc ? round_up(Nimg, kBlockM) : Nimg;
+  // ... unless there are at most 64 of them and the filter moves one pixel at a time along a row:
+  // then a tile is `hw_group` consecutive pixels of an output row x `hw_nbox` images
+  // (hw_nbox = 8, 16, 32 or 64, the smallest that holds the images)
+  int hw_nbox = kBlockM, hw_group = 1;
+  if (hwnc && Nimg <= 64 && d.stride_w == 1 && getenv("AMOSB_HWNC_NO_PACKING") == nullptr) {
+    hw_nbox = 8;
+    while (hw_nbox < Nimg) hw_nbox *= 2;
+    hw_group = kBlockM / hw_nbox;
+  }
   if (C % (16 / es) != 0 || Kout % (16 / es) != 0) {
     set_error("NHWC / HWNC conv2d needs C and K to be multiples of %d (16-byte rows for TMA); got "
               "C=%lld K=%lld", 16 / es, C, Kout);
     return AMOSB_ERR_UNSUPPORTED;
   }
-  const long long Mtot = Npad * P * Q;
+  const long long hw_qgroups = (Q + hw_group - 1) / hw_group;
+  const long long Mtot = hw_group > 1 ? P * hw_qgroups * kBlockM : Npad * P * Q;
   const long long Kd = R * S * C;
   if (Mtot > 0x7fffffffLL || Kd > 0x7fffffffLL) {
     set_error("conv2d problem too large");
@@ -1542,7 +1576,8 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
   if (hwnc) {
-    rc = encode_tiled_hwnc(&tmA, tma_dtype_for(d.in_dtype), es, const_cast<void*>(act), C, Nimg, W, H);
+    rc = encode_tiled_hwnc(&tmA, tma_dtype_for(d.in_dtype), es, const_cast<void*>(act), C, Nimg, W, H,
+                           hw_nbox, hw_group);
   } else {
     rc = encode_im2col_nhwc(&tmA, tma_dtype_for(d.in_dtype), const_cast<void*>(act), (int)Nimg, (int)H, (int)W, (int)C, d.pad_h,
                             d.pad_w, (int)R, (int)S, d.dil_h, d.dil_w, d.stride_h, d.stride_w, kBlockM, es);
@@ -1556,12 +1591,12 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   const int ob = d.out_dtype == AMOSB_F16 ? 2 : 4;
   const bool epi_tma = (Kout * ob) % 16 == 0 && getenv("AMOSB_DIRECT_STORE") == nullptr;
   if (epi_tma) {
-    rc = encode_tiled_3d(&tmC,
-                         d.out_dtype == AMOSB_F16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                         : d.out_dtype == AMOSB_S32 ? CU_TENSOR_MAP_DATA_TYPE_INT32
-                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                         ob, out, Kout, hwnc ? Nimg : Mtot, hwnc ? P * Q : 1, Kout * ob,
-                         (hwnc ? Nimg : Mtot) * Kout * ob, 128 / ob, 32);
+    const CUtensorMapDataType odt = d.out_dtype == AMOSB_F16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                    : d.out_dtype == AMOSB_S32 ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    rc = hwnc ? encode_store_hwnc(&tmC, odt, ob, out, Kout, Nimg, Q, P, hw_nbox)
+              : encode_tiled_3d(&tmC, odt, ob, out, Kout, Mtot, 1, Kout * ob, Mtot * Kout * ob,
+                                128 / ob, 32);
     if (rc != AMOSB_OK) return rc;
   }
   UmmaParams p;
@@ -1590,6 +1625,9 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   p.conv_C = (int)C;
   p.conv_N = (int)Npad;
   p.conv_N_real = (int)Nimg;
+  p.hw_group = hw_group;
+  p.hw_nbox = hw_nbox;
+  p.hw_qgroups = (int)hw_qgroups;
   p.stride_h = d.stride_h;
   p.stride_w = d.stride_w;
   p.pad_h = d.pad_h;

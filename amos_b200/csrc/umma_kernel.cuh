@@ -79,6 +79,10 @@ struct UmmaParams {
   int conv_C;    // NHWC / HWNC modes: channels (row pitch of the RSCK filter viewed as [R*S*C][K])
   int conv_N;    // HWNC mode: images per output pixel in the GEMM row index, padded to 128
   int conv_N_real;  // HWNC mode: images that exist (rows past them are computed on zeros, not stored)
+  // HWNC mode with fewer than 128 images: a 128-row tile is hw_group consecutive pixels of one
+  // output row x hw_nbox images (hw_group * hw_nbox = 128; hw_group = 1: the tile is 128 images
+  // of one pixel); hw_qgroups such tiles cover an output row
+  int hw_group, hw_nbox, hw_qgroups;
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int producers;   // 1..3 threads (in warps 0, 6, 7) issuing the TMA loads, k-blocks dealt round-robin
   const void* act;  // kModeConvPw: the NCHW activation (16-bit elements)
@@ -633,16 +637,25 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const int m0 = m_blk * kTileRows + mt * kBlockM;
-            int pq;
+            int pq, op, oq;
             if constexpr (MODE == kModeConvHwnc) {
-              pq = m0 / p.conv_N;            // output pixel of this sub-tile
-              cn[mt] = m0 - pq * p.conv_N;   // its first image
+              if (p.hw_group > 1) {
+                const int t = m0 / kBlockM;  // this sub-tile among the pixel groups
+                op = t / p.hw_qgroups;
+                oq = (t - op * p.hw_qgroups) * p.hw_group;  // first pixel of the group
+                cn[mt] = 0;
+              } else {
+                pq = m0 / p.conv_N;            // output pixel of this sub-tile
+                cn[mt] = m0 - pq * p.conv_N;   // its first image
+                op = pq / p.Q;
+                oq = pq - op * p.Q;
+              }
             } else {
               cn[mt] = m0 / p.PQ;
               pq = m0 - cn[mt] * p.PQ;
+              op = pq / p.Q;
+              oq = pq - op * p.Q;
             }
-            const int op = pq / p.Q;
-            const int oq = pq - op * p.Q;
             cw[mt] = oq * p.stride_w - p.pad_w;
             ch[mt] = op * p.stride_h - p.pad_h;
           }
@@ -943,13 +956,30 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       int orow = row;
       bool row_ok = row < p.M;
       int st_row = m_blk * kTileRows + mt * kBlockM + quarter * 32, st_batch = b;  // TMA-store box
+      int st_q = 0;  // HWNC: the box starts at image st_row of output pixel (st_batch, st_q)
       if constexpr (MODE == kModeConvHwnc) {
-        const int pix = row / p.conv_N;
-        const int img = row - pix * p.conv_N;
-        orow = pix * p.conv_N_real + img;
-        row_ok = row_ok && img < p.conv_N_real;
-        st_batch = st_row / p.conv_N;            // {K, images, pixels} map: clipped at the last image
-        st_row -= st_batch * p.conv_N;
+        if (p.hw_group > 1) {
+          const int t = st_row / kBlockM;  // pixel group of this 128-row accumulator tile
+          const int op = t / p.hw_qgroups;
+          const int q0 = (t - op * p.hw_qgroups) * p.hw_group;
+          const int r = quarter * 32 + static_cast<int>(lane);
+          const int g = r / p.hw_nbox, img = r - g * p.hw_nbox;
+          orow = (op * p.Q + q0 + g) * p.conv_N_real + img;
+          row_ok = row_ok && q0 + g < p.Q && img < p.conv_N_real;
+          st_batch = op;
+          st_q = q0 + (quarter * 32) / p.hw_nbox;
+          st_row = (quarter * 32) % p.hw_nbox;
+          if (st_q >= p.Q) st_row = p.conv_N_real;  // nothing of this warp exists (see below)
+        } else {
+          const int pix = row / p.conv_N;
+          const int img = row - pix * p.conv_N;
+          orow = pix * p.conv_N_real + img;
+          row_ok = row_ok && img < p.conv_N_real;
+          const int spix = st_row / p.conv_N;  // {K, images, Q, P} map: clipped at the last image
+          st_row -= spix * p.conv_N;
+          st_batch = spix / p.Q;
+          st_q = spix - st_batch * p.Q;
+        }
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                  static_cast<uint32_t>(acc * Cfg::kAccCols + mt * BN);
@@ -978,8 +1008,10 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       const int cols_left = p.N - n_blk * BN;
       int valid_chunks = row0 < p.M ? min(kChunks, (cols_left + 31) >> 5) : 0;
       if constexpr (MODE == kModeConvHwnc) {
-        if (st_row >= p.conv_N_real) valid_chunks = 0;  // all 32 rows of this warp are padding images
+        // all 32 rows of this warp are padding images, or pixels past the end of the output row
+        if (st_row >= p.conv_N_real) valid_chunks = 0;
       }
+      (void)st_q;
       if constexpr (EPI_TMA) {
         // registers -> 128B-swizzled staging rows -> one TMA store per 32 rows x 128 bytes.
         // The store engine clips rows >= M and columns >= N, and writes whole lines.
@@ -1030,7 +1062,11 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&tmC, buf, col0, st_row, st_batch);
+              if constexpr (MODE == kModeConvHwnc) {
+                tma_store_4d(&tmC, buf, col0, st_row, st_q, st_batch);
+              } else {
+                tma_store_3d(&tmC, buf, col0, st_row, st_batch);
+              }
               tma_store_commit();
             }
             epi_buf = epi_buf + 1 == kEpiBufs ? 0 : epi_buf + 1;

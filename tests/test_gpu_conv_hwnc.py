@@ -139,6 +139,45 @@ def test_image_counts_that_are_not_multiples_of_128(oracle, cfg):
     assert oracle.rel_l2(out.cpu().numpy(), np.maximum(ref + res, 0)) <= TOL_TE_LLVM
 
 
+@pytest.mark.parametrize("cfg", [
+    # H, W, N, C, K, R, S, stride_h (stride_w = 1 through the square stride 1), pad, dil
+    (6, 7, 8, 64, 72, 3, 3, 1, 1, 1),        # 16 pixels x 8 images per tile; 7 pixels per row: ragged groups
+    (9, 21, 12, 64, 40, 3, 3, 1, 1, 1),      # 12 images in boxes of 16; rows of 21 = 2 groups of 8 + 5
+    (5, 9, 32, 72, 136, 3, 3, 1, 2, 2),      # 4 pixels x 32 images; dilation; ragged channels
+    (4, 6, 64, 64, 264, 1, 1, 1, 0, 1),      # 2 pixels x 64 images; 1x1; three 128-wide filter tiles
+    (7, 5, 50, 32, 24, 5, 5, 1, 2, 1),       # 50 images in boxes of 64; 5x5 filter
+    (12, 12, 24, 128, 128, 3, 3, 1, 1, 1),
+])
+@pytest.mark.parametrize("cta_pair", [0, 3])
+def test_few_images_pack_pixels_into_a_tile(oracle, cfg, cta_pair):
+    """With at most 64 images (and a filter that moves one pixel at a time along a row) a 128-row tile
+    is several consecutive pixels of an output row x the images, instead of one pixel x images padded
+    to 128: the same sums as the padded form, bit for bit, TMA-store and plain-store epilogues."""
+    import os
+    h, w, n, c, k, r, s, st, pad, dil = cfg
+    rng = np.random.default_rng(n * 7 + c)
+    x = rng.uniform(-1, 1, (h, w, n, c)).astype(np.float16)
+    wt = rng.normal(0, 0.05, (r, s, c, k)).astype(np.float16)
+    d = _lib.conv2d_hwnc_desc(h, w, n, c, k, r, s, st, pad, dil, cta_pair=cta_pair)
+    assert "consecutive pixels of an output row" in _lib.describe_plan(d)
+    got = _run(x, wt, st, pad, dil, cta_pair=cta_pair)
+    assert oracle.rel_l2(got, oracle.c_conv2d_hwnc(x, wt, st, pad, dil, "te_llvm")) <= TOL_TE_LLVM
+    os.environ["AMOSB_HWNC_NO_PACKING"] = "1"
+    try:
+        assert "one output pixel x 128 images" in _lib.describe_plan(d)
+        padded = _run(x, wt, st, pad, dil, cta_pair=cta_pair)
+    finally:
+        del os.environ["AMOSB_HWNC_NO_PACKING"]
+    assert np.array_equal(got, padded)
+    os.environ["AMOSB_DIRECT_STORE"] = "1"
+    try:
+        assert np.array_equal(_run(x, wt, st, pad, dil, cta_pair=cta_pair), got)
+    finally:
+        del os.environ["AMOSB_DIRECT_STORE"]
+    got16 = _run(x, wt, st, pad, dil, out_dtype="float16", cta_pair=cta_pair)
+    assert np.array_equal(got16, got.astype(np.float16))
+
+
 def test_ragged_image_count_int8_and_tf32(oracle):
     rng = np.random.default_rng(3)
     h, w, n, c, k = 5, 6, 40, 32, 48
