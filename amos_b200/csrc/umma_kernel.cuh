@@ -428,6 +428,54 @@ __device__ __forceinline__ void store_nchw_quads(OutT* __restrict__ quad_dst, lo
   }
 }
 
+// ---- pieces of the epilogue shared by the single-CTA and the CTA-pair kernel -------------------
+// The accumulator leaves TMEM in chunks of 32 columns.  Loads are double-buffered: the load of
+// chunk c+1 is in flight while chunk c is converted and stored, so the TMEM read latency is paid
+// once per tile instead of once per chunk.  `process(registers, c)` is called for c = 0..nch-1.
+template <class F>
+__device__ __forceinline__ void for_each_chunk(uint32_t taddr_row, int nch, F&& process) {
+  uint32_t ra[32], rb[32];
+  if (nch > 0) tmem_ld_32x32b_x32(taddr_row, ra);
+#pragma unroll 1
+  for (int c = 0; c < nch; c += 2) {
+    tmem_ld_wait_regs(ra);
+    if (c + 1 < nch) tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>((c + 1) * 32), rb);
+    process(ra, c);
+    if (c + 1 < nch) {
+      tmem_ld_wait_regs(rb);
+      if (c + 2 < nch) tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>((c + 2) * 32), ra);
+      process(rb, c + 1);
+    }
+  }
+}
+
+// Element `off` of the fused addend (float32 or float16 in memory).
+__device__ __forceinline__ const void* addend_ptr(const UmmaParams& p, long long off) {
+  return p.addend_f16 ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
+                      : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
+}
+
+// 32 columns of one output row into the row's 128 bytes of a 128B-swizzled staging buffer
+// (`swz` = (row & 7) << 4).  32-bit outputs fill the row; 16-bit outputs fill half `h` of it.
+template <typename OutT>
+__device__ __forceinline__ void stage_chunk(uint32_t row_addr, uint32_t swz, int h,
+                                            const uint32_t (&r)[32]) {
+  if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      st_shared_v4(row_addr + ((static_cast<uint32_t>(j) << 4) ^ swz), r[4 * j], r[4 * j + 1],
+                   r[4 * j + 2], r[4 * j + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      st_shared_v4(row_addr + ((static_cast<uint32_t>(h * 4 + j) << 4) ^ swz),
+                   pack_half2(r[8 * j], r[8 * j + 1]), pack_half2(r[8 * j + 2], r[8 * j + 3]),
+                   pack_half2(r[8 * j + 4], r[8 * j + 5]), pack_half2(r[8 * j + 6], r[8 * j + 7]));
+    }
+  }
+}
+
 // A_MN_MAJOR: A is given as [K][M] (the `te` text indexes it A[k, i]) and consumed in place as an
 // MN-major operand, in chunks of 128 bytes of M like an MN-major B.  GEMM mode, MT = 1 only.
 template <int KIND, int BN, bool B_MN_MAJOR, int MODE, typename OutT, bool EPI_TMA, int MT = 1,
@@ -983,27 +1031,9 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                  static_cast<uint32_t>(acc * Cfg::kAccCols + mt * BN);
-      // The accumulator leaves TMEM in chunks of 32 columns.  Loads are double-buffered: the load
-      // of chunk c+1 is in flight while chunk c is converted and stored, so the TMEM read latency
-      // is paid once per tile instead of once per chunk.
       constexpr int kChunks = BN / 32;
       const int row0 = m_blk * kTileRows + mt * kBlockM + quarter * 32;  // first row of this warp
-      auto run_chunks = [&](int nch, auto&& process) {
-        uint32_t ra[32], rb[32];
-        if (nch > 0) tmem_ld_32x32b_x32(taddr_row, ra);
-#pragma unroll 1
-        for (int c = 0; c < nch; c += 2) {
-          tmem_ld_wait_regs(ra);
-          if (c + 1 < nch) tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>((c + 1) * 32), rb);
-          process(ra, c);
-          if (c + 1 < nch) {
-            tmem_ld_wait_regs(rb);
-            if (c + 2 < nch)
-              tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>((c + 2) * 32), ra);
-            process(rb, c + 1);
-          }
-        }
-      };
+      auto run_chunks = [&](int nch, auto&& process) { for_each_chunk(taddr_row, nch, process); };
       // chunks that hold columns < N (warp-uniform); none when all of the warp's rows are >= M
       const int cols_left = p.N - n_blk * BN;
       int valid_chunks = row0 < p.M ? min(kChunks, (cols_left + 31) >> 5) : 0;
@@ -1038,26 +1068,10 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                     ? static_cast<long long>(row)
                     : static_cast<long long>(b) * p.c_batch_stride +
                           static_cast<long long>(orow) * p.ldc + c0h;
-            const void* fp = p.addend_f16
-                                 ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
-                                 : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
+            const void* fp = addend_ptr(p, off);
             apply_trailing_ops<KIND>(r, p, c0h, p.N - c0h, row_ok, fp, 1);
           }
-          if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              st_shared_v4(row_addr + ((static_cast<uint32_t>(j) << 4) ^ swz), r[4 * j],
-                           r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              st_shared_v4(row_addr + ((static_cast<uint32_t>(h * 4 + j) << 4) ^ swz),
-                           pack_half2(r[8 * j], r[8 * j + 1]), pack_half2(r[8 * j + 2], r[8 * j + 3]),
-                           pack_half2(r[8 * j + 4], r[8 * j + 5]),
-                           pack_half2(r[8 * j + 6], r[8 * j + 7]));
-            }
-          }
+          stage_chunk<OutT>(row_addr, swz, h, r);
           if (h == kLoadsPerStore - 1) {
             fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the TMA engine
             __syncwarp();
@@ -1107,9 +1121,7 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
               off = (static_cast<long long>(ni) * p.N + col0) * p.PQ + (row - ni * p.PQ);
               stride = p.PQ;
             }
-            const void* fp = p.addend_f16
-                                 ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
-                                 : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
+            const void* fp = addend_ptr(p, off);
             apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row_ok, fp, stride);
           }
           if constexpr (kNchwOut) {
@@ -1124,10 +1136,17 @@ umma_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
               store_row_chunk<OutT>(row_ptr + col0, r, ncols_valid);
             } else {
               // NCHW: lanes of a warp are consecutive pixels of one channel plane -> coalesced.
+              // The epilogue of these kernels is bound by the instructions it issues, so the usual
+              // case of 32 channels that all exist carries no per-element test.
               OutT* dst = row_ptr + static_cast<long long>(col0) * p.PQ;
+              if (ncols_valid >= 32) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (j < ncols_valid) dst[static_cast<long long>(j) * p.PQ] = convert_acc<OutT>(r[j]);
+                for (int j = 0; j < 32; ++j) dst[static_cast<long long>(j) * p.PQ] = convert_acc<OutT>(r[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < ncols_valid) dst[static_cast<long long>(j) * p.PQ] = convert_acc<OutT>(r[j]);
+                }
               }
             }
           }

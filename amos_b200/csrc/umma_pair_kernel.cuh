@@ -415,24 +415,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = row0 + static_cast<int>(lane);
       const uint32_t taddr_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      // Double-buffered TMEM loads: chunk c+1 (32 columns) is in flight while chunk c is converted
-      // and stored.
-      auto run_chunks = [&](int nch, auto&& process) {
-        uint32_t ra[32], rb[32];
-        if (nch > 0) tmem_ld_32x32b_x32(taddr_row, ra);
-#pragma unroll 1
-        for (int c = 0; c < nch; c += 2) {
-          tmem_ld_wait_regs(ra);
-          if (c + 1 < nch) tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>((c + 1) * 32), rb);
-          process(ra, c);
-          if (c + 1 < nch) {
-            tmem_ld_wait_regs(rb);
-            if (c + 2 < nch)
-              tmem_ld_32x32b_x32(taddr_row + static_cast<uint32_t>((c + 2) * 32), ra);
-            process(rb, c + 1);
-          }
-        }
-      };
+      auto run_chunks = [&](int nch, auto&& process) { for_each_chunk(taddr_row, nch, process); };
       // chunks of this unit that hold columns < N (warp-uniform); none when all rows are >= M
       const int cols_left = p.N - (n_blk * BN + n_off);
       const int valid_chunks = row0 < p.M ? min(width >> 5, (cols_left + 31) >> 5) : 0;
@@ -460,26 +443,10 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     ? static_cast<long long>(row)
                     : static_cast<long long>(b) * p.c_batch_stride +
                           static_cast<long long>(row) * p.ldc + c0h;
-            const void* fp = p.addend_f16
-                                 ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
-                                 : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
+            const void* fp = addend_ptr(p, off);
             apply_trailing_ops<KIND>(r, p, c0h, p.N - c0h, row < p.M, fp, 1);
           }
-          if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              st_shared_v4(row_addr + ((static_cast<uint32_t>(j) << 4) ^ swz), r[4 * j],
-                           r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              st_shared_v4(row_addr + ((static_cast<uint32_t>(h * 4 + j) << 4) ^ swz),
-                           pack_half2(r[8 * j], r[8 * j + 1]), pack_half2(r[8 * j + 2], r[8 * j + 3]),
-                           pack_half2(r[8 * j + 4], r[8 * j + 5]),
-                           pack_half2(r[8 * j + 6], r[8 * j + 7]));
-            }
-          }
+          stage_chunk<OutT>(row_addr, swz, h, r);
           if (h == kLoadsPerStore - 1) {
             fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the TMA engine
             __syncwarp();
@@ -525,9 +492,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               off = (static_cast<long long>(ni) * p.N + col0) * p.PQ + (row - ni * p.PQ);
               stride = p.PQ;
             }
-            const void* fp = p.addend_f16
-                                 ? static_cast<const void*>(static_cast<const __half*>(p.addend) + off)
-                                 : static_cast<const void*>(static_cast<const float*>(p.addend) + off);
+            const void* fp = addend_ptr(p, off);
             apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row < p.M, fp, stride);
           }
           if constexpr (MODE == kModeConv) {
@@ -541,10 +506,18 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if constexpr (MODE != kModeConv) {
               store_row_chunk<OutT>(row_ptr + col0, r, ncols_valid);
             } else {
+              // NCHW: lanes of a warp are consecutive pixels of one channel plane -> coalesced.
+              // The epilogue of these kernels is bound by the instructions it issues, so the usual
+              // case of 32 channels that all exist carries no per-element test.
               OutT* dst = row_ptr + static_cast<long long>(col0) * p.PQ;
+              if (ncols_valid >= 32) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (j < ncols_valid) dst[static_cast<long long>(j) * p.PQ] = convert_acc<OutT>(r[j]);
+                for (int j = 0; j < 32; ++j) dst[static_cast<long long>(j) * p.PQ] = convert_acc<OutT>(r[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < ncols_valid) dst[static_cast<long long>(j) * p.PQ] = convert_acc<OutT>(r[j]);
+                }
               }
             }
           }
