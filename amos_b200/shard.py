@@ -11,6 +11,13 @@ The reference has no multi-device path at all (its "remote" measurement is TVM R
 device, reference: python/tvm/auto_tensorize/search/measure.py:793-981); this module is the one
 parallelism strategy added here.  An optional `gather_output` all-gathers the output shards over
 NCCL (NVLink) -- or gloo on CPU, which is how the host logic is tested without GPUs.
+
+`HostShardedCall` is the same split for operands that start in HOST memory every call.  There the
+replicated operand is the expensive part: eight ranks each copying all of B from their own host
+buffer push eight copies of it through one host's memory and PCIe.  Instead each rank copies the
+1/world slice of it that it is given over its own link and the ranks exchange the slices over
+NVLink (one all-gather): every byte of the operand crosses the host bus once per call, as on one
+GPU, and the all-gather is the one collective of the path.
 """
 from __future__ import annotations
 
@@ -116,3 +123,82 @@ def _as_nhwc(desc: _lib.AmosbOpDesc) -> _lib.AmosbOpDesc:
     d = desc.copy()
     d.kind = _lib.OP_CONV2D_NHWC
     return d
+
+
+def replicated_arg(desc: _lib.AmosbOpDesc):
+    """Index of the input every rank needs whole (B of a GEMM, the filter of a convolution), or
+    None (a batched GEMM splits both operands)."""
+    return None if desc.kind == _lib.OP_BATCHED_GEMM else desc.arg_b
+
+
+class HostShardedCall:
+    """One rank's part of a sharded call whose operands and result live in pinned host memory.
+
+    `host_inputs` are this rank's inputs as `shard_arrays` cuts them (its own rows / images, the
+    replicated operand whole); `host_output` receives this rank's rows.  Each `run()`:
+    copies the rank's own operand (and addend) to the GPU; copies ONE 1/world slice of the
+    replicated operand and all-gathers the slices over the process group when that operand is
+    large enough for it to matter (`min_gather_bytes`), else copies it whole; runs the kernels;
+    copies the rank's rows of the result back and waits for them.  Everything is queued on the
+    current stream, the copies from and to pinned memory asynchronously."""
+
+    def __init__(self, desc: _lib.AmosbOpDesc, host_inputs: Sequence, host_output, world: int,
+                 rank: int, device, group=None, min_gather_bytes: int = 1 << 20, prepare=None):
+        """`prepare(desc, inputs, outputs)` returns the object whose `run()` launches the kernels
+        on those device tensors (default: `device.PreparedCall`; tests without a GPU pass a
+        stand-in and `device="cpu"`)."""
+        import torch
+
+        if prepare is None:
+            from . import device as _device
+            prepare = _device.PreparedCall
+        self.world, self.rank, self.group = world, rank, group
+        self.desc = desc  # already the rank's local descriptor
+        self.host_inputs = list(host_inputs)
+        self.host_output = host_output
+        self.dev_inputs = [torch.empty(t.shape, dtype=t.dtype, device=device)
+                           for t in self.host_inputs]
+        self.dev_output = torch.empty(host_output.shape, dtype=host_output.dtype, device=device)
+        self.rep = replicated_arg(desc)
+        self.gathered = None
+        if self.rep is not None and world > 1:
+            full = self.host_inputs[self.rep]
+            nbytes = full.numel() * full.element_size()
+            if nbytes >= min_gather_bytes:
+                # byte slices of equal length (the last one padded): what this rank copies in
+                self.part_bytes = -(-nbytes // (world * 16)) * 16
+                self.flat_host = full.reshape(-1).view(torch.uint8)
+                self.gathered = torch.empty(self.part_bytes * world, dtype=torch.uint8,
+                                            device=device)
+                self.part = torch.zeros(self.part_bytes, dtype=torch.uint8, device=device)
+                self.dev_inputs[self.rep] = self.gathered[:nbytes].view(full.dtype).view(full.shape)
+                lo = min(rank * self.part_bytes, nbytes)
+                hi = min(lo + self.part_bytes, nbytes)
+                self.my_lo, self.my_hi = lo, hi
+        self.call = prepare(desc, self.dev_inputs, [self.dev_output])
+        self.launches_per_call = None
+        self.h2d_bytes = sum(t.numel() * t.element_size() for i, t in enumerate(self.host_inputs)
+                             if not (self.gathered is not None and i == self.rep))
+        if self.gathered is not None:
+            self.h2d_bytes += self.my_hi - self.my_lo
+        self.d2h_bytes = host_output.numel() * host_output.element_size()
+
+    def run(self) -> None:
+        import torch
+        import torch.distributed as dist
+        for i, (h, d) in enumerate(zip(self.host_inputs, self.dev_inputs)):
+            if self.gathered is not None and i == self.rep:
+                continue
+            d.copy_(h, non_blocking=True)
+        if self.gathered is not None:
+            n = self.my_hi - self.my_lo
+            if n > 0:
+                self.part[:n].copy_(self.flat_host[self.my_lo:self.my_hi], non_blocking=True)
+            if dist.get_backend(self.group) == "nccl":
+                dist.all_gather_into_tensor(self.gathered, self.part, group=self.group)
+            else:
+                dist.all_gather(list(self.gathered.chunk(self.world)), self.part, group=self.group)
+        self.launches_per_call = self.call.run()
+        self.host_output.copy_(self.dev_output, non_blocking=True)
+        if self.dev_output.is_cuda:
+            torch.cuda.current_stream(self.dev_output.device).synchronize()

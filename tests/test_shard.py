@@ -147,6 +147,36 @@ def _worker(rank, world, port, tmpdir):
         local = o.c_conv2d_hwnc(ins[0], ins[1], 1, 1, 1, "te_llvm")
         gathered = shard.gather_output(torch.from_numpy(local), wd)
         assert np.array_equal(gathered.numpy(), o.c_conv2d_hwnc(xw, ww, 1, 1, 1, "te_llvm"))
+        # operands in host memory: each rank copies its own rows of A and ONE slice of B, the
+        # slices are all-gathered, the (stand-in) kernel sees the whole B and the rank's rows
+        class _Fake:
+            def __init__(self, desc, ins, outs):
+                self.desc, self.ins, self.outs = desc, ins, outs
+
+            def run(self):
+                a_l, b_l = self.ins[0].numpy(), self.ins[1].numpy()
+                self.outs[0].copy_(torch.from_numpy(o.c_gemm(np.ascontiguousarray(a_l), b_l, "te_llvm")))
+                return 1
+
+        a2 = rng.uniform(-1, 1, (37, 24)).astype(np.float16)
+        b2 = rng.uniform(-1, 1, (24, 1000)).astype(np.float16)   # 48000 bytes: not a multiple of 2 x 16
+        full2 = _lib.gemm_desc(37, 1000, 24)
+        ld, ins, _ = shard.shard_arrays(full2, [a2, b2], [], world, rank)
+        host_out = torch.zeros((ld.m, 1000), dtype=torch.float32)
+        call = shard.HostShardedCall(ld, [torch.from_numpy(np.ascontiguousarray(x)) for x in ins],
+                                     host_out, world, rank, "cpu", min_gather_bytes=1024,
+                                     prepare=_Fake)
+        assert call.gathered is not None and call.h2d_bytes < a2.nbytes + b2.nbytes
+        for _ in range(2):
+            call.run()
+        gathered = shard.gather_output(host_out, full2)
+        assert np.array_equal(gathered.numpy(), o.c_gemm(a2, b2, "te_llvm"))
+        # a small replicated operand is copied whole, without the exchange
+        small = shard.HostShardedCall(ld, [torch.from_numpy(np.ascontiguousarray(x)) for x in ins],
+                                      host_out, world, rank, "cpu", prepare=_Fake)
+        assert small.gathered is None
+        small.run()
+        assert np.array_equal(shard.gather_output(host_out, full2).numpy(), o.c_gemm(a2, b2, "te_llvm"))
         # max-over-ranks reduction used for timing
         t = torch.tensor([float(rank + 1)])
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
