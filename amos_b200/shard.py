@@ -186,18 +186,24 @@ class HostShardedCall:
     def run(self) -> None:
         import torch
         import torch.distributed as dist
-        for i, (h, d) in enumerate(zip(self.host_inputs, self.dev_inputs)):
-            if self.gathered is not None and i == self.rep:
-                continue
-            d.copy_(h, non_blocking=True)
+        # the slice of the replicated operand first, so that its exchange over NVLink runs while the
+        # rank's own operand is still coming over PCIe
+        pending = None
         if self.gathered is not None:
             n = self.my_hi - self.my_lo
             if n > 0:
                 self.part[:n].copy_(self.flat_host[self.my_lo:self.my_hi], non_blocking=True)
             if dist.get_backend(self.group) == "nccl":
-                dist.all_gather_into_tensor(self.gathered, self.part, group=self.group)
+                pending = dist.all_gather_into_tensor(self.gathered, self.part, group=self.group,
+                                                      async_op=True)
             else:
                 dist.all_gather(list(self.gathered.chunk(self.world)), self.part, group=self.group)
+        for i, (h, d) in enumerate(zip(self.host_inputs, self.dev_inputs)):
+            if self.gathered is not None and i == self.rep:
+                continue
+            d.copy_(h, non_blocking=True)
+        if pending is not None:
+            pending.wait()  # the current stream waits for the exchange; the host does not
         self.launches_per_call = self.call.run()
         self.host_output.copy_(self.dev_output, non_blocking=True)
         if self.dev_output.is_cuda:
