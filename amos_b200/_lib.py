@@ -336,7 +336,8 @@ def conv2d_hwnc_desc(h: int, w: int, n: int, c: int, k: int, r: int, s: int, str
                      pad: int = 0, dilation: int = 1, out_dtype: int = AMOSB_F32,
                      tile_n: int = 0, cta_pair: int = 0, in_dtype: int = AMOSB_F16) -> AmosbOpDesc:
     """A[H,W,N,C] * B[R,S,C,K] -> Conv[P,Q,N,K]; operands consumed where they lie (a tile is one
-    output pixel x 128 images: image counts well below 128 waste tensor work)."""
+    output pixel x 128 images, or, for at most 64 images and stride 1 along W, several consecutive
+    pixels of an output row x the images)."""
     d = conv2d_desc(n, c, h, w, k, r, s, stride, pad, dilation, out_dtype, tile_n, cta_pair)
     d.kind = OP_CONV2D_HWNC
     _set_conv_in_dtype(d, in_dtype)

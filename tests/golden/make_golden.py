@@ -59,7 +59,79 @@ def _load_reference_helpers():
     conv = load("python/tvm/topi/testing/conv2d_nchw_python.py", "_ref_conv2d_nchw_python")
     bmm = load("python/tvm/topi/testing/batch_matmul.py", "_ref_batch_matmul")
     nhwc = load("python/tvm/topi/testing/conv2d_nhwc_python.py", "_ref_conv2d_nhwc_python")
+    global _dilate_python, _conv2d_hwcn_python
+    _dilate_python = load("python/tvm/topi/testing/dilate_python.py", "_ref_dilate_python").dilate_python
+    _conv2d_hwcn_python = load("python/tvm/topi/testing/conv2d_hwcn_python.py",
+                               "_ref_conv2d_hwcn_python").conv2d_hwcn_python
     return conv.conv2d_nchw_python, bmm.batch_matmul, nhwc.conv2d_nhwc_python
+
+
+_dilate_python = None
+_conv2d_hwcn_python = None
+
+
+def write_dilated_and_hwnc(conv2d_nchw_python, conv2d_nhwc_python):
+    """``ref_topi_dilated_and_hwnc.npz``: what the reference's helpers give for the two things the
+    files above do not reach.
+
+    * Dilation: the reference's tests dilate the FILTER with ``dilate_python`` (reference:
+      python/tvm/topi/testing/dilate_python.py:22-52) and run the undilated helper on it; the same
+      is done here for NCHW / KCRS and NHWC / RSCK, float16 and int8.
+    * HWNC: the reference has a helper for ``[H, W, C, N]`` activations and ``[P, Q, K, N]`` outputs
+      (``conv2d_hwcn_python``, python/tvm/topi/testing/conv2d_hwcn_python.py:24-78); an HWNC
+      problem is that one with the last two axes of activation and output exchanged.
+    """
+    rng = np.random.default_rng(20260007)
+    out = {}
+    dil_cases = [
+        # (layout, N, C, H, W, K, R, S, stride, pad, dil, kind)
+        ("nchw", 2, 16, 11, 9, 24, 3, 3, 1, 2, 2, "f16"),
+        ("nchw", 1, 8, 15, 15, 16, 3, 3, 2, 3, 3, "f16"),
+        ("nchw", 1, 16, 12, 12, 8, 3, 3, 1, 2, 2, "s8"),
+        ("nhwc", 2, 16, 11, 9, 24, 3, 3, 1, 2, 2, "f16"),
+        ("nhwc", 1, 32, 13, 13, 16, 3, 3, 1, 2, 2, "s8"),
+    ]
+    for i, (layout, n, c, h, w, k, r, s, st, pd, dl, kind) in enumerate(dil_cases):
+        if kind == "s8":
+            a = rng.integers(-128, 128, (n, c, h, w), dtype=np.int8)
+            wt = rng.integers(-128, 128, (k, c, r, s), dtype=np.int8)
+        else:
+            a = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float16)
+            wt = rng.normal(0, 0.05, (k, c, r, s)).astype(np.float16)
+        if layout == "nchw":
+            dw = _dilate_python(wt.astype(np.float64), (1, 1, dl, dl))
+            ref = conv2d_nchw_python(a.astype(np.float64), dw, st, pd)
+        else:
+            a = np.ascontiguousarray(a.transpose(0, 2, 3, 1))    # [N, H, W, C]
+            wt = np.ascontiguousarray(wt.transpose(2, 3, 1, 0))  # [R, S, C, K]
+            dw = _dilate_python(wt.astype(np.float64), (dl, dl, 1, 1))
+            ref = conv2d_nhwc_python(a.astype(np.float64), dw, st, pd)
+        out[f"dil{i}_layout"] = np.array(layout)
+        out[f"dil{i}_a"], out[f"dil{i}_w"] = a, wt
+        out[f"dil{i}_geom"] = np.array([st, pd, dl], dtype=np.int64)
+        out[f"dil{i}_out"] = ref
+    out["num_dil"] = np.array(len(dil_cases))
+    hwnc_cases = [
+        # (H, W, N, C, K, R, S, stride, pad, kind)
+        (7, 6, 5, 16, 24, 3, 3, 1, 1, "f16"),
+        (9, 9, 3, 8, 16, 3, 3, 2, 1, "f16"),
+        (6, 6, 4, 16, 16, 1, 1, 1, 0, "s8"),
+        (8, 7, 2, 32, 16, 3, 3, 1, 1, "s8"),
+    ]
+    for i, (h, w, n, c, k, r, s, st, pd, kind) in enumerate(hwnc_cases):
+        if kind == "s8":
+            a = rng.integers(-128, 128, (h, w, n, c), dtype=np.int8)
+            wt = rng.integers(-128, 128, (r, s, c, k), dtype=np.int8)
+        else:
+            a = rng.uniform(-1, 1, (h, w, n, c)).astype(np.float16)
+            wt = rng.normal(0, 0.05, (r, s, c, k)).astype(np.float16)
+        ref = _conv2d_hwcn_python(a.astype(np.float64).transpose(0, 1, 3, 2), wt.astype(np.float64),
+                                  st, pd)                      # [P, Q, K, N]
+        out[f"hwnc{i}_a"], out[f"hwnc{i}_w"] = a, wt
+        out[f"hwnc{i}_geom"] = np.array([st, pd, 1], dtype=np.int64)
+        out[f"hwnc{i}_out"] = np.ascontiguousarray(ref.transpose(0, 1, 3, 2))  # [P, Q, N, K]
+    out["num_hwnc"] = np.array(len(hwnc_cases))
+    np.savez_compressed(os.path.join(HERE, "ref_topi_dilated_and_hwnc.npz"), **out)
 
 
 def main():
@@ -138,6 +210,8 @@ def main():
         out[f"case{i}_out"] = ref  # float64; exact for the int8 cases
     out["num_cases"] = np.array(len(nhwc_cases))
     np.savez_compressed(os.path.join(HERE, "ref_topi_conv2d_nhwc.npz"), **out)
+
+    write_dilated_and_hwnc(conv2d_nchw_python, conv2d_nhwc_python)
 
     # ---- 2. known-answer vectors of the oracle --------------------------------------------
     rng = np.random.default_rng(20260002)

@@ -130,6 +130,47 @@ def test_against_reference_conv2d_nhwc_python(oracle, golden_dir):
     assert seen == {"float16", "int8", "float32"}
 
 
+def test_against_reference_dilation_and_hwcn_helpers(oracle, golden_dir):
+    """Dilated layers (the reference's tests dilate the filter with `dilate_python` and call the
+    undilated helper) and the HWNC layout (the reference's `conv2d_hwcn_python` with the last two
+    axes exchanged) pin the oracle's dilation arithmetic and its HWNC restatements: int8 bit for
+    bit, float16 to float32 rounding of the sums."""
+    g = np.load(os.path.join(golden_dir, "ref_topi_dilated_and_hwnc.npz"))
+    kinds = set()
+    for i in range(int(g["num_dil"])):
+        a, w, ref = g[f"dil{i}_a"], g[f"dil{i}_w"], g[f"dil{i}_out"]
+        stride, pad, dil = (int(v) for v in g[f"dil{i}_geom"])
+        assert dil > 1
+        layout = str(g[f"dil{i}_layout"])
+        kinds.add((layout, str(a.dtype)))
+        if layout == "nchw":
+            gots = [oracle.np_conv2d_nchw(a, w, stride, pad, dil, "exact")]
+            if a.dtype == np.float16:
+                gots.append(oracle.c_conv2d_nchw(a, w, stride, pad, dil, "exact"))
+        else:
+            gots = [oracle.np_conv2d_nhwc(a, w, stride, pad, dil, "exact")]
+            if a.dtype == np.float16:
+                gots.append(oracle.c_conv2d_nhwc(a, w, stride, pad, dil, "exact"))
+        for got in gots:
+            assert got.shape == ref.shape
+            if a.dtype == np.int8:
+                assert np.array_equal(got, ref.astype(np.int64))
+            else:
+                np.testing.assert_allclose(got, ref, rtol=2e-6, atol=1e-6)
+    assert kinds == {("nchw", "float16"), ("nchw", "int8"), ("nhwc", "float16"), ("nhwc", "int8")}
+    for i in range(int(g["num_hwnc"])):
+        a, w, ref = g[f"hwnc{i}_a"], g[f"hwnc{i}_w"], g[f"hwnc{i}_out"]
+        stride, pad, dil = (int(v) for v in g[f"hwnc{i}_geom"])
+        if a.dtype == np.int8:
+            got = oracle.np_conv2d_nhwc(np.ascontiguousarray(a.transpose(2, 0, 1, 3)), w, stride, pad,
+                                        dil, "exact").transpose(1, 2, 0, 3)
+            assert np.array_equal(got, ref.astype(np.int64))
+        else:
+            for got in (oracle.c_conv2d_hwnc(a, w, stride, pad, dil, "exact"),
+                        oracle.np_conv2d_hwnc(a, w, stride, pad, dil, "exact")):
+                np.testing.assert_allclose(got, ref, rtol=2e-6, atol=1e-6)
+
+
 def test_fp16_modes_are_close(oracle):
     """Rounding every product to fp16 moves the result by about 2^-11/sqrt(3) relative."""
     rng = np.random.default_rng(15)
