@@ -756,20 +756,21 @@ int amosb_describe_plan(const AmosbOpDesc* desc, int device, char* buf, int buf_
                  "%s<%s,BN=%d,conv-hwnc> tile %dx%dx%d = %d consecutive pixels of an output row x %d "
                  "images per accumulator, %d smem stages, tiled TMA A {%d channels, %d images, %d "
                  "pixels} under each filter tap + MN-major TMA B (RSCK as [R*S*C][K]), TMA-store "
-                 "epilogue, %lld tiles on %lld CTAs",
+                 "epilogue, %lld tiles on %lld %s",
                  dtype_name(desc->in_dtype), dtype_name(desc->out_dtype), fam, ck, bn, rows, bn, cbk,
-                 group, nbox, stages, cbk, nbox, group, tiles, tiles < slots ? tiles : slots);
+                 group, nbox, stages, cbk, nbox, group, tiles, tiles < slots ? tiles : slots,
+                 pair ? "CTA pairs" : "CTAs");
   } else if (desc->kind == AMOSB_OP_CONV2D_HWNC) {
     const long long m = ((desc->conv_n + 127) / 128) * 128 * desc->conv_p * desc->conv_q;
     const long long tiles = ((m + rows - 1) / rows) * ((desc->conv_k + bn - 1) / bn);
     n = snprintf(buf, buf_len,
                  "plan conv2d_hwnc %s->%s, operands in place (no re-layout, no workspace): [1] "
                  "%s<%s,BN=%d,conv-hwnc> tile %dx%dx%d = one output pixel x 128 images per "
-                 "accumulator, %d smem stages, tiled TMA A {%d channels, 128 images} of the input "
+                 "128 rows, %d smem stages, tiled TMA A {%d channels, 128 images} of the input "
                  "pixel under each filter tap + MN-major TMA B (RSCK as [R*S*C][K]), TMA-store "
-                 "epilogue, %lld tiles on %lld CTAs",
+                 "epilogue, %lld tiles on %lld %s",
                  dtype_name(desc->in_dtype), dtype_name(desc->out_dtype), fam, ck, bn, rows, bn, cbk,
-                 stages, cbk, tiles, tiles < slots ? tiles : slots);
+                 stages, cbk, tiles, tiles < slots ? tiles : slots, pair ? "CTA pairs" : "CTAs");
   } else if (desc->kind == AMOSB_OP_CONV2D_NHWC) {
     const long long m = desc->conv_n * desc->conv_p * desc->conv_q;
     const long long tiles = ((m + rows - 1) / rows) * ((desc->conv_k + bn - 1) / bn);

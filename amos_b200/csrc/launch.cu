@@ -789,14 +789,12 @@ static void plan_for_desc(const AmosbOpDesc& d, int sm_count, int* bn, bool* pai
   const long long kelems = d.in_dtype == AMOSB_S8 ? 128 : d.in_dtype == AMOSB_F32 ? 32 : 64;
   const long long kblocks = conv ? d.conv_r * d.conv_s * ((d.conv_c + kelems - 1) / kelems)
                                  : (d.k + kelems - 1) / kelems;
-  // A indexed [k,i] runs on single-CTA 128-row tiles only; HWNC on single-CTA tiles (128 or 256 rows)
-  // and so do float32 (tf32) and int8 convolutions other than NHWC
+  // A indexed [k,i] runs on single-CTA 128-row tiles only, and so do float32 (tf32) and int8 NCHW
+  // convolutions
   const bool single_only =
       (!conv && d.trans_a) ||
-      (conv && (d.in_dtype == AMOSB_F32 || d.in_dtype == AMOSB_S8) && d.kind != AMOSB_OP_CONV2D_NHWC);
-  int pair_mode = single_only ? 1 : d.cta_pair;
-  if (d.kind == AMOSB_OP_CONV2D_HWNC && !single_only && (pair_mode == 0 || pair_mode == 2))
-    pair_mode = 4;
+      (d.kind == AMOSB_OP_CONV2D_NCHW && (d.in_dtype == AMOSB_F32 || d.in_dtype == AMOSB_S8));
+  const int pair_mode = single_only ? 1 : d.cta_pair;
   choose_plan(i8_mn, tall_ok, batch, m, n, kblocks, d.tile_n, pair_mode, sm_count, bn, pairs, mt);
 }
 
@@ -1515,9 +1513,8 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     set_error("int8 conv2d writes int32");
     return AMOSB_ERR_UNSUPPORTED;
   }
-  // CTA pairs: float16 / bfloat16, and for NHWC also int8 and float32; tall tiles: float16 / bfloat16 only
-  if ((is_tf32 || is_i8) &&
-      (d.cta_pair == 3 || (d.cta_pair == 2 && d.kind != AMOSB_OP_CONV2D_NHWC))) {
+  // CTA pairs: every element type in both layouts; tall tiles: float16 / bfloat16 only
+  if ((is_tf32 || is_i8) && d.cta_pair == 3) {
     set_error("cta_pair=%d is not available for float32 (tf32) or int8 conv2d", d.cta_pair);
     return AMOSB_ERR_UNSUPPORTED;
   }
@@ -1572,7 +1569,7 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
   }
   int bn = 0, mt = 1;
   bool pairs = false;
-  plan_for_desc(d, st->sm_count, &bn, &pairs, &mt);  // HWNC: single-CTA families only
+  plan_for_desc(d, st->sm_count, &bn, &pairs, &mt);
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
   if (hwnc) {
@@ -1653,6 +1650,10 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     p.num_tiles = (int)(((Mtot + 2 * kBlockM - 1) / (2 * kBlockM)) * ((Kout + bn - 1) / bn));
     const int npairs8 = setup_schedule(&p, st, device, st->sm_count / 2, 2,
                                        static_cast<size_t>(kBlockM) * bn, workspace, workspace_bytes);
+    if (hwnc) {
+      if (epi_tma) return dispatch_pair_bn<1, true, kModeConvHwnc, int32_t, true>(bn, tmA, tmB, tmC, p, npairs8, stream);
+      return dispatch_pair_bn<1, true, kModeConvHwnc, int32_t, false>(bn, tmA, tmB, tmC, p, npairs8, stream);
+    }
     if (epi_tma) return dispatch_pair_bn<1, true, kModeConvNhwc, int32_t, true>(bn, tmA, tmB, tmC, p, npairs8, stream);
     return dispatch_pair_bn<1, true, kModeConvNhwc, int32_t, false>(bn, tmA, tmB, tmC, p, npairs8, stream);
   }
@@ -1661,6 +1662,10 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     p.num_tiles = (int)(((Mtot + 2 * kBlockM - 1) / (2 * kBlockM)) * ((Kout + bn - 1) / bn));
     const int npairs32 = setup_schedule(&p, st, device, st->sm_count / 2, 2,
                                         static_cast<size_t>(kBlockM) * bn, workspace, workspace_bytes);
+    if (hwnc) {
+      if (epi_tma) return dispatch_pair_bn<2, true, kModeConvHwnc, float, true>(bn, tmA, tmB, tmC, p, npairs32, stream);
+      return dispatch_pair_bn<2, true, kModeConvHwnc, float, false>(bn, tmA, tmB, tmC, p, npairs32, stream);
+    }
     if (epi_tma) return dispatch_pair_bn<2, true, kModeConvNhwc, float, true>(bn, tmA, tmB, tmC, p, npairs32, stream);
     return dispatch_pair_bn<2, true, kModeConvNhwc, float, false>(bn, tmA, tmB, tmC, p, npairs32, stream);
   }
@@ -1681,6 +1686,14 @@ int run_conv2d_nhwc(const AmosbOpDesc& d, const void* act, const void* flt, cons
     p.num_tiles = (int)tiles_pair;
     const int npairs = setup_schedule(&p, st, device, st->sm_count / 2, 2,
                                       static_cast<size_t>(kBlockM) * bn, workspace, workspace_bytes);
+    if (hwnc) {
+      if (epi_tma) {
+        if (f32) return dispatch_pair_bn<0, true, kModeConvHwnc, float, true>(bn, tmA, tmB, tmC, p, npairs, stream);
+        return dispatch_pair_bn<0, true, kModeConvHwnc, __half, true>(bn, tmA, tmB, tmC, p, npairs, stream);
+      }
+      if (f32) return dispatch_pair_bn<0, true, kModeConvHwnc, float, false>(bn, tmA, tmB, tmC, p, npairs, stream);
+      return dispatch_pair_bn<0, true, kModeConvHwnc, __half, false>(bn, tmA, tmB, tmC, p, npairs, stream);
+    }
     if (epi_tma) {
       if (f32) return dispatch_pair_bn<0, true, kModeConvNhwc, float, true>(bn, tmA, tmB, tmC, p, npairs, stream);
       return dispatch_pair_bn<0, true, kModeConvNhwc, __half, true>(bn, tmA, tmB, tmC, p, npairs, stream);

@@ -39,8 +39,9 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int kStages = Cfg::kStages;
   constexpr int kElemsPer128B = (KIND == 0) ? 64 : (KIND == 1) ? 128 : 32;
   constexpr int kUmmaKRows = (KIND == 0) ? 16 : (KIND == 1) ? 32 : 8;
-  static_assert(KIND != 2 || MODE == kModeGemm || MODE == kModeConvNhwc,
-                "float32 (tf32) pairs: GEMM and NHWC convolution");
+  static_assert(KIND != 2 || MODE == kModeGemm || MODE == kModeConvNhwc || MODE == kModeConvHwnc,
+                "float32 (tf32) pairs: GEMM and NHWC / HWNC convolution");
+  static_assert(MODE != kModeConvHwnc || B_MN_MAJOR, "HWNC conv reads the RSCK filter MN-major");
   constexpr int kMmaPerStage = 4;
   constexpr uint32_t kBChunkBytes = kElemsPer128B * 128;
   constexpr int kBChunksPerCta = (BN / 2) / kElemsPer128B;  // MN-major chunks this CTA loads
@@ -157,10 +158,27 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int cw = 0, ch = 0, cn = 0;
         int cc = 0, fs = 0, fr = 0;  // channel chunk and filter tap of k-block kb
         if constexpr (MODE != kModeGemm) {
-          cn = m0 / p.PQ;
-          const int pq = m0 - cn * p.PQ;
-          const int op = pq / p.Q;
-          const int oq = pq - op * p.Q;
+          int op, oq;
+          if constexpr (MODE == kModeConvHwnc) {
+            // this CTA's 128 rows: 128 images of one output pixel, or (few images) a group of
+            // consecutive pixels of an output row x the images -- as in the single-CTA kernel
+            if (p.hw_group > 1) {
+              const int t = m0 / kBlockM;
+              op = t / p.hw_qgroups;
+              oq = (t - op * p.hw_qgroups) * p.hw_group;
+              cn = 0;
+            } else {
+              const int pq = m0 / p.conv_N;
+              cn = m0 - pq * p.conv_N;
+              op = pq / p.Q;
+              oq = pq - op * p.Q;
+            }
+          } else {
+            cn = m0 / p.PQ;
+            const int pq = m0 - cn * p.PQ;
+            op = pq / p.Q;
+            oq = pq - op * p.Q;
+          }
           cw = oq * p.stride_w - p.pad_w;
           ch = op * p.stride_h - p.pad_h;
           const int rs = (sg.kb_begin + kb) / p.c_chunks;
@@ -199,9 +217,16 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           } else {
-            tma_load_im2col_4d_pair(sA, &tmA, fb, cc * kElemsPer128B, cw, ch, cn,
-                                    static_cast<uint16_t>(fs * p.dil_w),
-                                    static_cast<uint16_t>(fr * p.dil_h));
+            if constexpr (MODE == kModeConvHwnc) {
+              // {channels, images, w, h}: padding and rows past the last pixel are out-of-range
+              // coordinates -> zeros
+              tma_load_4d_pair(sA, &tmA, fb, cc * kElemsPer128B, cn, cw + fs * p.dil_w,
+                               ch + fr * p.dil_h);
+            } else {
+              tma_load_im2col_4d_pair(sA, &tmA, fb, cc * kElemsPer128B, cw, ch, cn,
+                                      static_cast<uint16_t>(fs * p.dil_w),
+                                      static_cast<uint16_t>(fr * p.dil_h));
+            }
             if constexpr (MODE == kModeConv) {
               for (int j = 0; j * 64 < half; ++j) {
                 tma_load_2d_pair(sB + j * 64 * 128, &tmB, fb, kabs * kElemsPer128B, n_half0 + j * 64);
@@ -413,12 +438,46 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const int row0 = m_blk * kPairM + static_cast<int>(rank) * kBlockM + quarter * 32;
       const int row = row0 + static_cast<int>(lane);
+      // row of the output matrix this thread holds and whether it exists; HWNC: a GEMM row is
+      // (pixel, image), laid out as in the single-CTA kernel (see there)
+      int orow = row;
+      bool row_ok = row < p.M;
+      int st_row = row0, st_batch = b, st_q = 0;  // where this warp's TMA-store box starts
+      if constexpr (MODE == kModeConvHwnc) {
+        if (p.hw_group > 1) {
+          const int t = row0 / kBlockM;
+          const int op = t / p.hw_qgroups;
+          const int q0 = (t - op * p.hw_qgroups) * p.hw_group;
+          const int r = quarter * 32 + static_cast<int>(lane);
+          const int g = r / p.hw_nbox, img = r - g * p.hw_nbox;
+          orow = (op * p.Q + q0 + g) * p.conv_N_real + img;
+          row_ok = row_ok && q0 + g < p.Q && img < p.conv_N_real;
+          st_batch = op;
+          st_q = q0 + (quarter * 32) / p.hw_nbox;
+          st_row = (quarter * 32) % p.hw_nbox;
+          if (st_q >= p.Q) st_row = p.conv_N_real;  // nothing of this warp exists
+        } else {
+          const int pix = row / p.conv_N;
+          const int img = row - pix * p.conv_N;
+          orow = pix * p.conv_N_real + img;
+          row_ok = row_ok && img < p.conv_N_real;
+          const int spix = row0 / p.conv_N;
+          st_row = row0 - spix * p.conv_N;
+          st_batch = spix / p.Q;
+          st_q = spix - st_batch * p.Q;
+        }
+      }
+      (void)st_q;
       const uint32_t taddr_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
       auto run_chunks = [&](int nch, auto&& process) { for_each_chunk(taddr_row, nch, process); };
       // chunks of this unit that hold columns < N (warp-uniform); none when all rows are >= M
       const int cols_left = p.N - (n_blk * BN + n_off);
-      const int valid_chunks = row0 < p.M ? min(width >> 5, (cols_left + 31) >> 5) : 0;
+      int valid_chunks = row0 < p.M ? min(width >> 5, (cols_left + 31) >> 5) : 0;
+      if constexpr (MODE == kModeConvHwnc) {
+        // all 32 rows of this warp are padding images, or pixels past the end of the output row
+        if (st_row >= p.conv_N_real) valid_chunks = 0;
+      }
       if constexpr (EPI_TMA) {
         constexpr int kColsPerStore = 128 / static_cast<int>(sizeof(OutT));
         constexpr int kLoadsPerStore = kColsPerStore / 32;
@@ -442,16 +501,20 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 (p.epi_flags & kEpiAddRowVec)
                     ? static_cast<long long>(row)
                     : static_cast<long long>(b) * p.c_batch_stride +
-                          static_cast<long long>(row) * p.ldc + c0h;
+                          static_cast<long long>(orow) * p.ldc + c0h;
             const void* fp = addend_ptr(p, off);
-            apply_trailing_ops<KIND>(r, p, c0h, p.N - c0h, row < p.M, fp, 1);
+            apply_trailing_ops<KIND>(r, p, c0h, p.N - c0h, row_ok, fp, 1);
           }
           stage_chunk<OutT>(row_addr, swz, h, r);
           if (h == kLoadsPerStore - 1) {
             fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&tmC, buf, col0, row0, b);
+              if constexpr (MODE == kModeConvHwnc) {
+                tma_store_4d(&tmC, buf, col0, st_row, st_q, st_batch);
+              } else {
+                tma_store_3d(&tmC, buf, col0, row0, b);
+              }
               tma_store_commit();
             }
             epi_buf = epi_buf + 1 == kEpiBufs ? 0 : epi_buf + 1;
@@ -463,7 +526,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bool quad_ok = false;
         if constexpr (MODE != kModeConv) {
           row_ptr = out + static_cast<long long>(b) * p.c_batch_stride +
-                    static_cast<long long>(row) * p.ldc;
+                    static_cast<long long>(orow) * p.ldc;
         } else {
           const int n_img = row / p.PQ;
           const int pq = row - n_img * p.PQ;
@@ -485,7 +548,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               off = (p.epi_flags & kEpiAddRowVec)
                         ? static_cast<long long>(row)
                         : static_cast<long long>(b) * p.c_batch_stride +
-                              static_cast<long long>(row) * p.ldc + col0;
+                              static_cast<long long>(orow) * p.ldc + col0;
               stride = 1;
             } else {
               const int ni = row / p.PQ;
@@ -493,7 +556,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               stride = p.PQ;
             }
             const void* fp = addend_ptr(p, off);
-            apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row < p.M, fp, stride);
+            apply_trailing_ops<KIND>(r, p, col0, ncols_valid, row_ok, fp, stride);
           }
           if constexpr (MODE == kModeConv) {
             if (p.nchw_quads) {  // warp-uniform
@@ -502,7 +565,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               return;
             }
           }
-          if (row < p.M) {
+          if (row_ok) {
             if constexpr (MODE != kModeConv) {
               store_row_chunk<OutT>(row_ptr + col0, r, ncols_valid);
             } else {

@@ -50,7 +50,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("cfg", CASES)
-@pytest.mark.parametrize("cta_pair", [1, 3])
+@pytest.mark.parametrize("cta_pair", [1, 2, 3])
 def test_conv2d_hwnc(oracle, cfg, cta_pair):
     h, w, n, c, k, r, s, st, pad, dil = cfg
     rng = np.random.default_rng(h * 100 + c + k)
@@ -148,7 +148,7 @@ def test_image_counts_that_are_not_multiples_of_128(oracle, cfg):
     (7, 5, 50, 32, 24, 5, 5, 1, 2, 1),       # 50 images in boxes of 64; 5x5 filter
     (12, 12, 24, 128, 128, 3, 3, 1, 1, 1),
 ])
-@pytest.mark.parametrize("cta_pair", [0, 3])
+@pytest.mark.parametrize("cta_pair", [0, 2, 3])
 def test_few_images_pack_pixels_into_a_tile(oracle, cfg, cta_pair):
     """With at most 64 images (and a filter that moves one pixel at a time along a row) a 128-row tile
     is several consecutive pixels of an output row x the images, instead of one pixel x images padded
@@ -176,6 +176,44 @@ def test_few_images_pack_pixels_into_a_tile(oracle, cfg, cta_pair):
         del os.environ["AMOSB_DIRECT_STORE"]
     got16 = _run(x, wt, st, pad, dil, out_dtype="float16", cta_pair=cta_pair)
     assert np.array_equal(got16, got.astype(np.float16))
+
+
+@pytest.mark.parametrize("n", [256, 200, 24])
+def test_cta_pairs_match_single_cta_tiles(oracle, n):
+    """HWNC on CTA pairs (each CTA of a pair holds one 128-row group: 128 images of a pixel, or a
+    group of pixels x few images): bit-identical to the single-CTA tiles, for float16, int8 and
+    float32 tensors."""
+    rng = np.random.default_rng(n)
+    h, w, c, k = 6, 7, 64, 272
+    for kind in ("f16", "s8", "f32"):
+        if kind == "s8":
+            x = rng.integers(-128, 128, (h, w, n, c), dtype=np.int8)
+            wt = rng.integers(-128, 128, (3, 3, c, k), dtype=np.int8)
+            in_dtype, odt = _lib.AMOSB_S8, torch.int32
+        elif kind == "f32":
+            x = rng.uniform(-1, 1, (h, w, n, c)).astype(np.float32)
+            wt = rng.normal(0, 0.05, (3, 3, c, k)).astype(np.float32)
+            in_dtype, odt = _lib.AMOSB_F32, torch.float32
+        else:
+            x = rng.uniform(-1, 1, (h, w, n, c)).astype(np.float16)
+            wt = rng.normal(0, 0.05, (3, 3, c, k)).astype(np.float16)
+            in_dtype, odt = _lib.AMOSB_F16, torch.float32
+        outs = []
+        for pair in (2, 1):
+            d = _lib.conv2d_hwnc_desc(h, w, n, c, k, 3, 3, 1, 1, 1, tile_n=256, cta_pair=pair,
+                                      in_dtype=in_dtype)
+            assert ("umma_pair" in _lib.describe_plan(d)) == (pair == 2)
+            out = torch.full((h, w, n, k), 77, dtype=odt, device=DEV)
+            assert device.run(d, [_t(x), _t(wt)], [out]) == 1
+            assert device.status_peek(0) == 0
+            outs.append(out.cpu().numpy())
+        assert np.array_equal(outs[0], outs[1]), kind
+        if kind == "s8":
+            want = oracle.np_conv2d_nhwc(np.ascontiguousarray(x.transpose(2, 0, 1, 3)), wt, 1, 1, 1,
+                                         "exact").transpose(1, 2, 0, 3)
+            assert np.array_equal(outs[0], want)
+        elif kind == "f16":
+            assert oracle.rel_l2(outs[0], oracle.c_conv2d_hwnc(x, wt, 1, 1, 1, "te_llvm")) <= TOL_TE_LLVM
 
 
 def test_ragged_image_count_int8_and_tf32(oracle):
