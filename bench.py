@@ -82,9 +82,9 @@ WORKLOADS = {
     # ... and in its HWNC / RSCK layout (same file, :74-104); images are not the outermost axis, so
     # these run on one GPU only
     "conv_hwnc_c3b_28x28_n256_c128_k128_3x3": dict(
-        _conv(256, 128, 28, 28, 128, 3, 3, 1, 1, "hwnc"), seed=20260002, wdist="normal", shard=False),
+        _conv(256, 128, 28, 28, 128, 3, 3, 1, 1, "hwnc"), seed=20260002, wdist="normal", shard=True),
     "conv_hwnc_c3c_14x14_n256_c256_k256_3x3": dict(
-        _conv(256, 256, 14, 14, 256, 3, 3, 1, 1, "hwnc"), seed=20260002, wdist="normal", shard=False),
+        _conv(256, 256, 14, 14, 256, 3, 3, 1, 1, "hwnc"), seed=20260002, wdist="normal", shard=True),
 }
 HEADLINE = "gemm_f16_4096"
 
@@ -440,7 +440,10 @@ def measure_workload(name, steps, warmup, world, rank, dev, sampler=None, e2e_st
                             device.get_workspace(_lib.workspace_bytes(full), dev)).run()
         calls[0].run()  # the shard again, after the workspace may have been replaced
         torch.cuda.synchronize(dev)
-        want = full_out[start:start + count]
+        if full.kind == _lib.OP_CONV2D_HWNC:  # images are the third axis of [P, Q, N, K]
+            want = full_out[:, :, start:start + count]
+        else:
+            want = full_out[start:start + count]
         exact = bool(torch.equal(local_out, want))
         rel = 0.0
         if not exact:
