@@ -1247,7 +1247,15 @@ long long tail_workspace_bytes(const AmosbOpDesc& d) {
   } else if (conv) {
     long long nimg = d.conv_n;
     if (d.kind == AMOSB_OP_CONV2D_HWNC && nimg > 1) nimg = (nimg + kBlockM - 1) / kBlockM * kBlockM;
-    const long long m = nimg * d.conv_p * d.conv_q;
+    long long m = nimg * d.conv_p * d.conv_q;
+    if (d.kind == AMOSB_OP_CONV2D_HWNC && d.conv_n > 1 && d.conv_n <= 64 && d.stride_w == 1 &&
+        getenv("AMOSB_HWNC_NO_PACKING") == nullptr) {
+      // few images: a 128-row group is several pixels of an output row x the images
+      int nbox = 8;
+      while (nbox < d.conv_n) nbox *= 2;
+      const long long group = kBlockM / nbox;
+      m = d.conv_p * ((d.conv_q + group - 1) / group) * kBlockM;
+    }
     tiles = ((m + rows - 1) / rows) * ((d.conv_k + bn - 1) / bn);
     kb = d.conv_r * d.conv_s * ((d.conv_c + kelems - 1) / kelems);
   } else {

@@ -140,6 +140,8 @@ CONVS = [
     ("nhwc", 9, 136, 14, 14, 264, 3, 1, 128, 3),
     ("hwnc", 128, 72, 6, 6, 136, 3, 1, 128, 3),
     ("hwnc", 128, 72, 6, 6, 136, 3, 1, 64, 1),
+    ("hwnc", 24, 72, 9, 10, 136, 3, 1, 128, 1),    # few images: pixels packed into a tile
+    ("hwnc", 16, 136, 12, 14, 264, 3, 1, 256, 2),  # the same on CTA pairs
 ]
 
 
