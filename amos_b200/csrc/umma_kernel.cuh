@@ -34,7 +34,10 @@ constexpr int umma_threads(int mode) { return mode == 4 ? kNumThreadsPw : kNumTh
 // and are not stored), so a 128-row tile is one output pixel
 // times 128 consecutive images: its A operand for a filter tap is a plain tiled box
 // {64 channels, 128 images} of the input pixel (p*st + r*dil - pad, q*st + s*dil - pad), and a
-// pixel outside the image is an out-of-range coordinate that the load fills with zeros.
+// pixel outside the image is an out-of-range coordinate that the load fills with zeros.  With at
+// most 64 images and stride 1 along W the images are padded to 8, 16, 32 or 64 instead and a
+// 128-row tile is that many images x 128 / that many consecutive pixels of an output row (box
+// {64 channels, images, pixels, 1}; UmmaParams::hw_group / hw_nbox / hw_qgroups).
 // kModeConvPw: 1x1, stride-1, unpadded NCHW convolution consumed in place when the channel planes
 // are not 16-byte multiples (so that no tensor map can describe them): GEMM rows are the pixels
 // (n, p, q) flattened, the activation [C][P*Q] of an image is an MN-major A operand that four extra

@@ -1,5 +1,7 @@
 // CTA-pair variant of the persistent tcgen05 kernel: a cluster of two CTAs (two SMs) computes one
-// 256 (M) x BN (N) tile with tcgen05.mma.cta_group::2.
+// 256 (M) x BN (N) tile with tcgen05.mma.cta_group::2.  Modes: GEMM, NCHW convolution on the
+// re-laid-out operands (16-bit elements), NHWC and HWNC convolution in place; kinds f16 / bf16,
+// int8 and tf32 (the latter two: GEMM and the in-place convolutions).
 //
 // Each CTA of the pair owns 128 rows of the tile: it loads its own 128-row A tile and HALF of the
 // B tile (BN/2 columns), and holds the 128 x BN accumulator of its rows in its own TMEM.  The MMA
