@@ -140,3 +140,50 @@ def test_pinned_and_pageable_host_memory_give_the_same_result():
     finally:
         del os.environ["AMOSB_HOST_CHUNKS"]
     assert np.array_equal(pc.numpy(), want)
+
+
+def test_host_sharded_call_as_one_rank_and_as_two_on_one_gpu(tmp_path):
+    """shard.HostShardedCall on pinned host operands: as a single rank (no exchange) and as the
+    two ranks of a one-process group taken in turn on this one GPU with the exchange replaced by
+    its result (each rank's slice of B copied into place by hand) -- the slicing, the buffer
+    views and the copies are what is under test; the collective itself runs in the two-rank CPU
+    test and in the multi-GPU benchmark."""
+    from amos_b200 import shard
+    rng = np.random.default_rng(12)
+    m, n, k = 300, 520, 264
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float16)
+    full = _lib.gemm_desc(m, n, k)
+    want = _device_result(full, [a, b], (m, n))
+    # one rank
+    out = torch.zeros((m, n), dtype=torch.float32).pin_memory()
+    call = shard.HostShardedCall(full, [torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()],
+                                 out, 1, 0, DEV)
+    assert call.gathered is None and call.h2d_bytes == a.nbytes + b.nbytes
+    call.run()
+    assert np.array_equal(out.numpy(), want)
+    # two ranks, one after the other: B arrives as two byte slices
+    got = np.zeros((m, n), np.float32)
+    for rank in range(2):
+        ld, ins, _ = shard.shard_arrays(full, [a, b], [], 2, rank)
+        start, count = shard.partition(m, 2, rank)
+        o = torch.zeros((count, n), dtype=torch.float32).pin_memory()
+
+        class _NoExchange(shard.HostShardedCall):
+            def run(self):  # what run() does, with the all-gather replaced by both slices copied in
+                flat = self.flat_host
+                self.gathered[:flat.numel()].copy_(flat, non_blocking=True)
+                for i, (h, d) in enumerate(zip(self.host_inputs, self.dev_inputs)):
+                    if i != self.rep:
+                        d.copy_(h, non_blocking=True)
+                self.call.run()
+                self.host_output.copy_(self.dev_output, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+
+        c2 = _NoExchange(ld, [torch.from_numpy(np.ascontiguousarray(x)).pin_memory() for x in ins], o,
+                         2, rank, DEV, min_gather_bytes=1024)
+        assert c2.gathered is not None and c2.part_bytes * 2 >= b.nbytes
+        assert c2.my_hi - c2.my_lo == min(c2.part_bytes, b.nbytes - rank * c2.part_bytes)
+        c2.run()
+        got[start:start + count] = o.numpy()
+    assert np.array_equal(got, want)
